@@ -18,7 +18,7 @@ import torch
 
 from ..csrc import build as _build
 from ..csrc import cdecl as _cdecl
-from ..parts.base import CacheSpec, FixedStateSpec, PagedKVSpec
+from ..parts.base import CacheSpec, FixedStateSpec, PagedKVSpec, paged_part, state_part
 
 
 class CacheError(RuntimeError):
@@ -222,8 +222,9 @@ class CacheManager(PageTable):
         kinds: List[Tuple[int, int]] = []          # (window, kept first tokens) of each group
         members: List[List[int]] = []
         self.layer_group: List[int] = []
-        for i, sp in enumerate(specs):
-            if isinstance(sp, PagedKVSpec):
+        for i, spec in enumerate(specs):
+            sp = paged_part(spec)
+            if sp is not None:
                 kind = (sp.window, sp.keep_first if sp.window > 0 else 0)
                 if kind not in kinds:
                     kinds.append(kind)
@@ -246,8 +247,9 @@ class CacheManager(PageTable):
         self.k: List[Optional[torch.Tensor]] = []
         self.v: List[Optional[torch.Tensor]] = []
         self.state: List[Optional[torch.Tensor]] = []
-        for sp in specs:
-            if isinstance(sp, PagedKVSpec):
+        for spec in specs:            # a layer may keep pages, a state slot, both (`CombinedSpec`) or nothing
+            sp, st = paged_part(spec), state_part(spec)
+            if sp is not None:
                 # one page more than the manager hands out: the "null page", where padding tokens
                 # of a captured step write their keys and values
                 shape = (num_pages + 1, sp.kv_heads, page_size, sp.head_dim)
@@ -258,16 +260,14 @@ class CacheManager(PageTable):
                     self.v.append(self.k[-1])
                 else:
                     self.v.append(torch.zeros(shape[:3] + (sp.value_dim,), dtype=dtype, device=device))
-                self.state.append(None)
-            elif isinstance(sp, FixedStateSpec):
-                self.k.append(None)
-                self.v.append(None)
-                # one slot more than there are requests: the spare slot, which padding rows of a
-                # captured step use so that they never touch a live request's state
-                self.state.append(torch.zeros((max_requests + 1,) + tuple(sp.shape), dtype=sp.dtype, device=device))
             else:
                 self.k.append(None)
                 self.v.append(None)
+            if st is not None:
+                # one slot more than there are requests: the spare slot, which padding rows of a
+                # captured step use so that they never touch a live request's state
+                self.state.append(torch.zeros((max_requests + 1,) + tuple(st.shape), dtype=st.dtype, device=device))
+            else:
                 self.state.append(None)
 
     def admit(self, rid: int) -> int:
@@ -294,7 +294,7 @@ class CacheManager(PageTable):
 
     def bytes_per_token(self) -> int:
         n = 0
-        for sp in self.specs:
-            if isinstance(sp, PagedKVSpec):
+        for sp in map(paged_part, self.specs):
+            if sp is not None:
                 n += sp.kv_heads * (sp.head_dim + (0 if sp.values_are_keys else sp.value_dim)) * torch.empty((), dtype=self.dtype).element_size()
         return n

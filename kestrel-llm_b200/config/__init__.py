@@ -3,8 +3,9 @@ from .registry import (Architecture, architecture_of, known_architectures, load_
                        register_architecture, resolve_architecture)
 from .zidivik_config import ZidivikConfig
 from .tidavik_config import TidavikConfig
+from .toredra_config import ToredraConfig
 from .engine_options import EngineOptions
 
-__all__ = ["ConfigError", "ModelConfig", "Qwen3Config", "ZidivikConfig", "TidavikConfig", "read_config_json", "Architecture",
+__all__ = ["ConfigError", "ModelConfig", "Qwen3Config", "ZidivikConfig", "TidavikConfig", "ToredraConfig", "read_config_json", "Architecture",
            "architecture_of", "known_architectures", "load_config", "register_architecture",
            "resolve_architecture", "EngineOptions"]

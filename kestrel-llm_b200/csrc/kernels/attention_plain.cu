@@ -19,8 +19,8 @@
 // `gate`, float32 [T, nq], multiplies each head's output.
 //
 // A layer may also change the scores and the way keys are weighed (`ScoreOpts`, attention_score.cuh):
-// a cap, a logarithmic distance term, a softmax with a valueless extra term exp(0) in its
-// denominator - it enters the merge as one more state (max 0, sum 1, out 0) in front of the warps'
+// a cap, a logarithmic distance term, a softmax with a valueless extra term exp(sink) in its
+// denominator (sink a number per head, or 0) - it enters the merge as one more state (max sink, sum 1, out 0) in front of the warps'
 // - or sigmoid weights that are not normalised, where the states are plain sums.
 #include "common.cuh"
 #include "attention_score.cuh"
@@ -129,10 +129,10 @@ attention_plain_kernel(const T *__restrict__ q, const T *__restrict__ k_cache, c
     __syncthreads();
     if (warp == 0) {
         const bool sink = opts.weighting == KESTREL_WEIGH_SOFTMAX_SINK;
-        float M = sink ? 0.f : -INFINITY;
+        float M = sink ? score.sink : -INFINITY;
 #pragma unroll
         for (int w = 0; w < PA_WARPS; ++w) M = fmaxf(M, sm_m[w]);
-        float L = sink ? expf(0.f - M) : 0.f;
+        float L = sink ? expf(score.sink - M) : 0.f;
         float o[PA_MAX_PER_LANE];
 #pragma unroll
         for (int c = 0; c < PA_MAX_PER_LANE; ++c) o[c] = 0.f;
@@ -165,10 +165,11 @@ KESTREL_API int kestrel_attention_plain_scored(const void *q, const void *k_cach
                                                const int *block_table, int table_stride, int page_size,
                                                void *out, int dtype, int T, int nq, int nkv, int hd, int vd, int window,
                                                int keep_first, const float *gate, float scale, float softcap, const float *r1,
-                                               const float *r2, const float *head_bias, int weighting, cudaStream_t stream) {
+                                               const float *r2, const float *head_bias, int weighting, const float *sink,
+                                               cudaStream_t stream) {
     if (T == 0) return 0;
     KESTREL_REQUIRE(weighting >= 0 && weighting <= 2 && softcap >= 0.f && (r1 == nullptr) == (r2 == nullptr), "attention_plain: bad score options");
-    const ScoreOpts opts = {softcap, r1, r2, head_bias, weighting};
+    const ScoreOpts opts = {softcap, r1, r2, head_bias, weighting, sink};
     KESTREL_REQUIRE(T > 0 && nq > 0 && nkv > 0 && hd > 0 && vd > 0 && keep_first >= 0, "attention_plain: bad sizes");
     KESTREL_REQUIRE(hd <= 32 * PA_MAX_PER_LANE && vd <= 32 * PA_MAX_PER_LANE, "attention_plain: head size %d / %d exceeds %d", hd, vd, 32 * PA_MAX_PER_LANE);
     KESTREL_REQUIRE(nq <= 65535, "attention_plain: %d query heads exceed the grid", nq);
@@ -191,7 +192,7 @@ KESTREL_API int kestrel_attention_plain_ex(const void *q, const void *k_cache, c
                                            int keep_first, const float *gate, float scale, cudaStream_t stream) {
     return kestrel_attention_plain_scored(q, k_cache, v_cache, positions, seq_of_token, block_table, table_stride, page_size, out, dtype, T,
                                           nq, nkv, hd, vd, window, keep_first, gate, scale, 0.f, nullptr, nullptr, nullptr, KESTREL_WEIGH_SOFTMAX,
-                                          stream);
+                                          nullptr, stream);
 }
 
 KESTREL_API int kestrel_attention_plain(const void *q, const void *k_cache, const void *v_cache,

@@ -9,6 +9,9 @@
 //   `qk_norm` = 2: the same over the whole q projection (all nq * hd columns at once) and the whole k
 //            projection, with weights [nq * hd] and [nkv * hd]; `qk_norm` = 0 leaves them as they are;
 //   `v_norm`: v <- v / sqrt(mean(v^2) + eps) per head, no weight (it is cached so);
+//   `inv_freq` given: q and k (after their norm) are turned by position - pair j of a head's first `rot` dimensions
+//            by the angle position * inv_freq[j] (float32), `rot_mode` 0 pairing dimension j with j + rot / 2, 1 pairing
+//            2j with 2j + 1; `rot_scale` multiplies cos and sin; the rest of a head passes unchanged;
 //   q -> q_out in the storage type; k, v -> the token's slot in its request's pages;
 //   gate_out[t, h] = sigmoid(gate column h), float32.
 // One warp a head row (the blocks of a token share its head rows out), lanes over the head's
@@ -55,8 +58,10 @@ attn_prepare_ex_kernel(const float *__restrict__ partial, int S, size_t slice_st
                        const int *__restrict__ positions, const int *__restrict__ seq_of_token,
                        const int *__restrict__ block_table, int table_stride, int page_size,
                        T *__restrict__ k_cache, T *__restrict__ v_cache, T *__restrict__ q_out, float *__restrict__ gate_out,
-                       int nq, int nkv, int hd, int vd, int has_kv, const float *__restrict__ bias, int v_norm, int keep_x) {
+                       int nq, int nkv, int hd, int vd, int has_kv, const float *__restrict__ bias, int v_norm, int keep_x,
+                       const float *__restrict__ inv_freq, int rot, int rot_mode, float rot_scale) {
     extern __shared__ float apx_ss[];              // qk_norm = 2: sum of squares of every q and k head, then (keep_x) their columns
+    __shared__ float apx_rot[APX_WARPS][32 * APX_PER_LANE];   // rotate-half pairing: a warp's head, so that a lane reaches its partner
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -88,8 +93,8 @@ attn_prepare_ex_kernel(const float *__restrict__ partial, int S, size_t slice_st
         mul_k = 1.0f / sqrtf(tk / (float)(nkv * hd) + eps);
     }
     size_t slot_row = 0;
+    const int pos = positions[t];
     if (has_kv) {
-        const int pos = positions[t];
         const int page = block_table[(size_t)seq_of_token[t] * table_stride + pos / page_size];
         slot_row = (size_t)page * nkv * page_size + (pos % page_size);      // + kv head * page_size
     }
@@ -131,7 +136,37 @@ attn_prepare_ex_kernel(const float *__restrict__ partial, int S, size_t slice_st
 #pragma unroll
         for (int c = 0; c < APX_PER_LANE; ++c) {
             const int i = lane + 32 * c;
-            if (i < n) dst[i] = from_f32<T>(w ? x[c] * mul * w[i] : x[c] * mul);
+            x[c] = i < n ? (w ? x[c] * mul * w[i] : x[c] * mul) : 0.f;
+        }
+        if (inv_freq && kind != 2) {                // the branch is the same for the whole warp
+            const int half = rot / 2;
+            if (rot_mode == 0) {
+#pragma unroll
+                for (int c = 0; c < APX_PER_LANE; ++c) apx_rot[warp][lane + 32 * c] = x[c];
+                __syncwarp();
+            }
+#pragma unroll
+            for (int c = 0; c < APX_PER_LANE; ++c) {
+                const int i = lane + 32 * c;
+                // interleaved pairs sit in neighbouring lanes; every lane takes part in the exchange
+                const float other = rot_mode == 0 ? apx_rot[warp][i < half ? min(i + half, 32 * APX_PER_LANE - 1) : max(i - half, 0)]
+                                                  : __shfl_xor_sync(0xffffffffu, x[c], 1);
+                if (i < rot) {
+                    const bool first = rot_mode == 0 ? i < half : (i & 1) == 0;
+                    const int j = rot_mode == 0 ? (i < half ? i : i - half) : i >> 1;
+                    float sn, cs;
+                    sincosf((float)pos * inv_freq[j], &sn, &cs);
+                    sn *= rot_scale;
+                    cs *= rot_scale;
+                    x[c] = first ? x[c] * cs - other * sn : x[c] * cs + other * sn;
+                }
+            }
+            if (rot_mode == 0) __syncwarp();        // the next head of this warp writes the same rows
+        }
+#pragma unroll
+        for (int c = 0; c < APX_PER_LANE; ++c) {
+            const int i = lane + 32 * c;
+            if (i < n) dst[i] = from_f32<T>(x[c]);
         }
     }
     if (gate_out && blockIdx.y == 0) {
@@ -149,7 +184,20 @@ KESTREL_API int kestrel_attn_prepare_normed(const float *partial, int S, long lo
                                             const int *seq_of_token, const int *block_table, int table_stride, int page_size,
                                             void *k_cache, void *v_cache, void *q_out, float *gate_out, int dtype, int T, int nq,
                                             int nkv, int hd, int vd, int has_kv, cudaStream_t stream) {
+    return kestrel_attn_prepare_rotated(partial, S, slice_stride, ld, bias, q_norm_w, k_norm_w, qk_norm, v_norm, norm_eps, nullptr, 0, 0, 1.f,
+                                        positions, seq_of_token, block_table, table_stride, page_size, k_cache, v_cache, q_out, gate_out, dtype,
+                                        T, nq, nkv, hd, vd, has_kv, stream);
+}
+
+KESTREL_API int kestrel_attn_prepare_rotated(const float *partial, int S, long long slice_stride, int ld, const float *bias, const float *q_norm_w,
+                                             const float *k_norm_w, int qk_norm, int v_norm, float norm_eps, const float *inv_freq, int rot,
+                                             int rot_mode, float rot_scale, const int *positions, const int *seq_of_token,
+                                             const int *block_table, int table_stride, int page_size, void *k_cache, void *v_cache,
+                                             void *q_out, float *gate_out, int dtype, int T, int nq, int nkv, int hd, int vd, int has_kv,
+                                             cudaStream_t stream) {
     if (T == 0) return 0;
+    KESTREL_REQUIRE(!inv_freq || (rot > 0 && rot % 2 == 0 && rot <= hd && (rot_mode == 0 || rot_mode == 1)),
+                    "attn_prepare_ex: %d rotated dimensions of a head of %d (mode %d)", rot, hd, rot_mode);
     KESTREL_REQUIRE(qk_norm >= 0 && qk_norm <= 2, "attn_prepare_ex: qk_norm %d is none of 0, 1, 2", qk_norm);
     KESTREL_REQUIRE(qk_norm != 2 || (q_norm_w && (k_norm_w || !has_kv)), "attn_prepare_ex: the norm over a whole projection needs its weights");
     size_t smem = qk_norm == 2 ? (size_t)(nq + nkv) * sizeof(float) : 0;
@@ -165,11 +213,11 @@ KESTREL_API int kestrel_attn_prepare_normed(const float *partial, int S, long lo
     const int by = T >= 512 ? 1 : (n_heads + APX_WARPS - 1) / APX_WARPS;
     if (dtype == KESTREL_F32)
         kestrel_launch(attn_prepare_ex_kernel<float>, dim3(T, by), dim3(APX_WARPS * 32), smem, stream, partial, S, (size_t)slice_stride, ld, q_norm_w, k_norm_w, qk_norm, norm_eps,
-                       positions, seq_of_token, block_table, table_stride, page_size, (float *)k_cache, (float *)v_cache, (float *)q_out, gate_out, nq, nkv, hd, vd, has_kv, bias, v_norm, keep_x);
+                       positions, seq_of_token, block_table, table_stride, page_size, (float *)k_cache, (float *)v_cache, (float *)q_out, gate_out, nq, nkv, hd, vd, has_kv, bias, v_norm, keep_x, inv_freq, rot, rot_mode, rot_scale);
     else if (dtype == KESTREL_BF16)
         kestrel_launch(attn_prepare_ex_kernel<__nv_bfloat16>, dim3(T, by), dim3(APX_WARPS * 32), smem, stream, partial, S, (size_t)slice_stride, ld, q_norm_w, k_norm_w, qk_norm, norm_eps,
                        positions, seq_of_token, block_table, table_stride, page_size, (__nv_bfloat16 *)k_cache, (__nv_bfloat16 *)v_cache, (__nv_bfloat16 *)q_out, gate_out, nq, nkv,
-                       hd, vd, has_kv, bias, v_norm, keep_x);
+                       hd, vd, has_kv, bias, v_norm, keep_x, inv_freq, rot, rot_mode, rot_scale);
     else
         return kestrel_fail(-2, "attn_prepare_ex: unknown dtype %d", dtype);
     return kestrel_check_launch("attn_prepare_ex");

@@ -4,7 +4,8 @@
 //   s <- cap * tanh(s / cap)                      if cap > 0
 //   s <- s - r1[head] * ln(1 + r2[head] * (i - j))   if r1 is given (i the query's position, j the key's)
 //   weighting 0: softmax over the visible keys
-//             1: softmax with one more term exp(0) in the denominator that carries no value
+//             1: softmax with one more term in the denominator that carries no value: exp(sink[head]) where a
+//                layer has learned numbers for it, exp(0) otherwise
 //             2: each visible key weighs sigmoid(s + head_bias[head]); nothing is normalised over keys
 #pragma once
 #include <math.h>
@@ -18,11 +19,13 @@ struct ScoreOpts {
     const float *r1, *r2;      // [nq] each, or both null
     const float *head_bias;    // [nq] or null; read by weighting 2 only
     int weighting;
+    const float *sink;         // [nq] or null (= zeros); read by weighting 1 only
 };
 
 // the options of one head, fetched once
 struct HeadScore {
     float cap, inv_cap, r1, r2, bias;
+    float sink;                // the extra term's exponent (weighting 1), as the scores are: not in base-2 units
     bool dist;
     __device__ __forceinline__ HeadScore(const ScoreOpts &o, int head) {
         cap = o.softcap;
@@ -31,6 +34,7 @@ struct HeadScore {
         r1 = dist ? o.r1[head] : 0.f;
         r2 = dist ? o.r2[head] : 0.f;
         bias = (o.weighting == KESTREL_WEIGH_SIGMOID && o.head_bias) ? o.head_bias[head] : 0.f;
+        sink = (o.weighting == KESTREL_WEIGH_SOFTMAX_SINK && o.sink) ? o.sink[head] : 0.f;
     }
     // s = q . k * scale of a key `distance` positions behind the query
     __device__ __forceinline__ float operator()(float s, int distance) const {

@@ -446,7 +446,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             size_t qrow = write ? (size_t)(tok_begin + row / G) * p.nq + kvh * G + row % G : 0;
             float inv = p.slices > 1 ? 1.f : 1.0f / l_run;
             if (sigmoid) inv = 1.f;
-            if (sink) inv = 1.0f / (l_run + at_exp2(0.f - m_ref));     // one more term exp(0), against the same reference
+            if (sink) inv = 1.0f / (l_run + at_exp2(hs.sink * 1.4426950408889634f - m_ref));     // one more term exp(sink), against the same reference
 #pragma unroll
             for (int c = 0; c < 128; c += 32) {
                 uint32_t o[32];
@@ -516,7 +516,7 @@ KESTREL_API int kestrel_attention_tc(const void *q, const void *k_cache, const v
                                      cudaStream_t stream) {
     return kestrel_attention_tc_scored(q, k_cache, v_cache, out, part_o, part_ml, tile_seq, tile_row0, tiles, rows_per_tile, cu_seqlens, kv_lens,
                                        block_table, table_width, table_stride, page_size, cache_pages, T, nq, nkv, hd, window, slices, slice_len,
-                                       max_kv_ptr, scale, 0.f, nullptr, nullptr, nullptr, KESTREL_WEIGH_SOFTMAX, stream);
+                                       max_kv_ptr, scale, 0.f, nullptr, nullptr, nullptr, KESTREL_WEIGH_SOFTMAX, nullptr, stream);
 }
 
 // The same with a layer's options on the scores and on the weighing of keys (attention_score.cuh); with
@@ -526,7 +526,8 @@ KESTREL_API int kestrel_attention_tc_scored(const void *q, const void *k_cache, 
                                             int tiles, int rows_per_tile, const int *cu_seqlens, const int *kv_lens, const int *block_table,
                                             int table_width, int table_stride, int page_size, int cache_pages, int T, int nq, int nkv, int hd,
                                             int window, int slices, int slice_len, const int *max_kv_ptr, float scale, float softcap,
-                                            const float *r1, const float *r2, const float *head_bias, int weighting, cudaStream_t stream) {
+                                            const float *r1, const float *r2, const float *head_bias, int weighting, const float *sink,
+                                            cudaStream_t stream) {
     if (T == 0 || tiles == 0) return 0;
     const bool scored = softcap > 0.f || r1 != nullptr || weighting != KESTREL_WEIGH_SOFTMAX;
     KESTREL_REQUIRE(weighting >= 0 && weighting <= 2 && softcap >= 0.f && (r1 == nullptr) == (r2 == nullptr), "attention_tc: bad score options");
@@ -553,7 +554,7 @@ KESTREL_API int kestrel_attention_tc_scored(const void *q, const void *k_cache, 
     p.max_kv_ptr = max_kv_ptr;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.scale = scale;
-    p.opts = {softcap, r1, r2, head_bias, weighting};
+    p.opts = {softcap, r1, r2, head_bias, weighting, sink};
     p.scored = scored ? 1 : 0;
     size_t smem = 12 * AT_PANEL + 8 * B_COUNT + 16 + 1024;
     static bool attr_set = false;

@@ -27,7 +27,7 @@
 //
 // A layer may change the scores and the weighing of keys (`ScoreOpts`, attention_score.cuh): a cap and a
 // logarithmic distance term on the float32 scores; a softmax whose denominator has a valueless extra
-// term exp(0), added where a row's states are closed; or sigmoid weights that are not normalised,
+// term exp(sink[head]) (exp(0) without learned numbers), added where a row's states are closed; or sigmoid weights that are not normalised,
 // which need no running maximum - P is the weights themselves.  Without options the scores keep the
 // short path (one multiply into the exponent's base-2 scale).
 //
@@ -280,9 +280,10 @@ attention_window_kernel(const AwParams p) {
             const int row = row0 + r, tok = tok_begin + row / G, head = kvh * G + row % G;
             float inv = 1.0f / l_r[h2];
             if (sigmoid) inv = 1.0f;
-            if (sink) {                                   // one more state in front: maximum 0, sum 1, no value
-                const float M = fmaxf(m_r[h2], 0.f), f = fast_exp2(m_r[h2] - M);
-                inv = f / (fast_exp2(0.f - M) + l_r[h2] * f);
+            if (sink) {                                   // one more state in front: maximum sink, sum 1, no value
+                const float s2 = (p.opts.sink ? p.opts.sink[head] : 0.f) * 1.4426950408889634f;
+                const float M = fmaxf(m_r[h2], s2), f = fast_exp2(m_r[h2] - M);
+                inv = f / (fast_exp2(s2 - M) + l_r[h2] * f);
             }
             if (p.gate) inv *= p.gate[(size_t)tok * p.nq + head];
             __nv_bfloat16 *dst = p.out + ((size_t)tok * p.nq + head) * vd;
@@ -334,10 +335,11 @@ attention_window_kernel(const AwParams p) {
         }
         for (int idx = tid; idx < rows_here * vd; idx += AW_THREADS) {
             const int r = idx / vd, col = idx % vd;
-            float M = sink ? 0.f : -INFINITY;
+            const float s2 = (sink && p.opts.sink) ? p.opts.sink[kvh * G + (row0 + r) % G] * 1.4426950408889634f : 0.f;
+            float M = sink ? s2 : -INFINITY;
 #pragma unroll
             for (int w = 0; w < KW; ++w) M = fmaxf(M, sm_m[w * 16 + r]);
-            float L = sink ? fast_exp2(0.f - M) : 0.f, acc = 0.f;
+            float L = sink ? fast_exp2(s2 - M) : 0.f, acc = 0.f;
 #pragma unroll
             for (int w = 0; w < KW; ++w) {
                 if (sigmoid) { acc += sm_o[((size_t)w * 16 + r) * D + col]; continue; }
@@ -372,11 +374,12 @@ attention_window_merge_kernel(const AwParams p, int ksplit, int D) {
         const int s = threadIdx.x;
         const float m = s < ksplit ? p.part_ml[(base + (size_t)s * 16) * 2] : -INFINITY;
         const float l = s < ksplit ? p.part_ml[(base + (size_t)s * 16) * 2 + 1] : 0.f;
+        const float s2 = (sink && p.opts.sink) ? p.opts.sink[kvh * G + row % G] * 1.4426950408889634f : 0.f;
         float M = warp_max(m);
-        if (sink) M = fmaxf(M, 0.f);
+        if (sink) M = fmaxf(M, s2);
         const float f = m == -INFINITY ? 0.f : fast_exp2(m - M);
         if (s < ksplit) f_s[s] = sigmoid ? 1.f : f;
-        float L = sink ? fast_exp2(0.f - M) : 0.f;
+        float L = sink ? fast_exp2(s2 - M) : 0.f;
         for (int k = 0; k < ksplit; ++k) L += __shfl_sync(0xffffffffu, l * f, k);
         if (s == 0) f_s[ksplit] = sigmoid ? 1.f : 1.0f / L;
     }
@@ -446,14 +449,14 @@ KESTREL_API int kestrel_attention_window(const void *q, const void *k_cache, con
                                          int nseq, int max_count, int nq, int nkv, int hd, int vd, int window, int keep_first, float scale,
                                          cudaStream_t stream) {
     return kestrel_attention_window_scored(q, k_cache, v_cache, out, gate, cu_seqlens, kv_lens, block_table, table_stride, page_size, nseq, max_count,
-                                           nq, nkv, hd, vd, window, keep_first, scale, 0.f, nullptr, nullptr, nullptr, KESTREL_WEIGH_SOFTMAX, 1, nullptr, stream);
+                                           nq, nkv, hd, vd, window, keep_first, scale, 0.f, nullptr, nullptr, nullptr, KESTREL_WEIGH_SOFTMAX, nullptr, 1, nullptr, stream);
 }
 
 KESTREL_API int kestrel_attention_window_scored(const void *q, const void *k_cache, const void *v_cache, void *out, const float *gate,
                                                 const int *cu_seqlens, const int *kv_lens, const int *block_table, int table_stride, int page_size,
                                                 int nseq, int max_count, int nq, int nkv, int hd, int vd, int window, int keep_first, float scale,
                                                 float softcap, const float *r1, const float *r2, const float *head_bias, int weighting,
-                                                int ksplit, float *scratch, cudaStream_t stream) {
+                                                const float *sink, int ksplit, float *scratch, cudaStream_t stream) {
     if (nseq == 0 || max_count == 0) return 0;
     KESTREL_REQUIRE(ksplit >= 1 && ksplit <= 65535 && (ksplit == 1 || scratch), "attention_window: %d shares of the keys without scratch", ksplit);
     KESTREL_REQUIRE(weighting >= 0 && weighting <= 2 && softcap >= 0.f && (r1 == nullptr) == (r2 == nullptr), "attention_window: bad score options");
@@ -478,7 +481,7 @@ KESTREL_API int kestrel_attention_window_scored(const void *q, const void *k_cac
     p.keep_first = window > 0 ? keep_first : 0;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.scale = scale;
-    p.opts = {softcap, r1, r2, head_bias, weighting};
+    p.opts = {softcap, r1, r2, head_bias, weighting, sink};
     p.scored = softcap > 0.f || r1 != nullptr || weighting != KESTREL_WEIGH_SOFTMAX;
     const int D = max(hd, vd), G = nq / nkv;
     const bool keys_mode = (long long)max_count * G <= AW_KEYS_MODE_ROWS;

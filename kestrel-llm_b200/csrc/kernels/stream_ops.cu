@@ -167,3 +167,194 @@ KESTREL_API int kestrel_partial_columns(const float *p, int S, long long slice_s
         return kestrel_fail(-2, "partial_columns: unknown dtype %d", dtype);
     return kestrel_check_launch("partial_columns");
 }
+
+// ------------------------------------------------------------------------------------------
+// The same with an activation on the summed columns: 0 none, 1 the square of relu, 2 tanh, 3 silu.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ float column_act(float z, int act) {
+    if (act == 1) { const float r = fmaxf(z, 0.f); return r * r; }
+    if (act == 2) return tanhf(z);
+    if (act == 3) return z / (1.0f + expf(-z));
+    return z;
+}
+
+template <typename TOut>
+__global__ void partial_columns_act_kernel(const float *__restrict__ p, int S, size_t slice_stride, int ld, int col0,
+                                           const float *__restrict__ bias, int act, TOut *__restrict__ out, int n, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    size_t t = idx / n;
+    int i = (int)(idx % n);
+    float z = sum_slices(p, S, slice_stride, t * ld + col0 + i);
+    if (bias) z += bias[col0 + i];
+    out[idx] = from_f32<TOut>(column_act(z, act));
+}
+
+KESTREL_API int kestrel_partial_columns_act(const float *p, int S, long long slice_stride, int ld, int col0, const float *bias, int act, void *out,
+                                            int dtype, int T, int n, cudaStream_t stream) {
+    if (T == 0) return 0;
+    KESTREL_REQUIRE(T > 0 && n > 0 && S > 0 && col0 >= 0 && col0 + n <= ld && act >= 0 && act <= 3, "partial_columns_act: bad sizes or activation %d", act);
+    size_t total = (size_t)T * n;
+    unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == KESTREL_F32)
+        kestrel_launch(partial_columns_act_kernel<float>, dim3(blocks), dim3(256), 0, stream, p, S, (size_t)slice_stride, ld, col0, bias, act, (float *)out, n, total);
+    else if (dtype == KESTREL_BF16)
+        kestrel_launch(partial_columns_act_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, p, S, (size_t)slice_stride, ld, col0, bias, act, (__nv_bfloat16 *)out, n, total);
+    else
+        return kestrel_fail(-2, "partial_columns_act: unknown dtype %d", dtype);
+    return kestrel_check_launch("partial_columns_act");
+}
+
+// ------------------------------------------------------------------------------------------
+// Block-wide sum in a fixed tree: lanes by shuffle, warps in ascending order.  Every thread gets it.
+// ------------------------------------------------------------------------------------------
+#define GN_THREADS 256
+__device__ __forceinline__ float gn_block_sum(float v, float *red) {
+    v = warp_sum(v);
+    __syncthreads();                                  // red may still be read from the sum before
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int k = 0; k < GN_THREADS / 32; ++k) tot += red[k];
+    return tot;
+}
+
+// ------------------------------------------------------------------------------------------
+// Two products side by side, each normalised over the row with a weight of its own, then mixed:
+// out[t] = mix * (a / sqrt(mean(a^2) + eps) * wa + b / sqrt(mean(b^2) + eps) * wb), float32.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(GN_THREADS)
+combine_normed_kernel(const float *__restrict__ a, int Sa, size_t stride_a, const float *__restrict__ wa, const float *__restrict__ b, int Sb,
+                      size_t stride_b, const float *__restrict__ wb, float eps, float mix, float *__restrict__ out, int d) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float cn_rows[];               // a's row, then b's
+    __shared__ float red[GN_THREADS / 32];
+    const int t = blockIdx.x;
+    float *ra = cn_rows, *rb = cn_rows + d;
+    float sa = 0.f, sb = 0.f;
+    for (int i = threadIdx.x; i < d; i += GN_THREADS) {
+        const float x = sum_slices(a, Sa, stride_a, (size_t)t * d + i), y = sum_slices(b, Sb, stride_b, (size_t)t * d + i);
+        ra[i] = x;
+        rb[i] = y;
+        sa = fmaf(x, x, sa);
+        sb = fmaf(y, y, sb);
+    }
+    const float na = 1.0f / sqrtf(gn_block_sum(sa, red) / (float)d + eps);
+    const float nb = 1.0f / sqrtf(gn_block_sum(sb, red) / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += GN_THREADS) out[(size_t)t * d + i] = mix * (ra[i] * na * wa[i] + rb[i] * nb * wb[i]);
+}
+
+KESTREL_API int kestrel_combine_normed(const float *a, int Sa, long long stride_a, const float *wa, const float *b, int Sb, long long stride_b,
+                                       const float *wb, float eps, float mix, float *out, int T, int d, cudaStream_t stream) {
+    if (T == 0) return 0;
+    KESTREL_REQUIRE(T > 0 && d > 0 && Sa > 0 && Sb > 0 && d <= 12000, "combine_normed: bad sizes T=%d d=%d", T, d);
+    kestrel_launch(combine_normed_kernel, dim3(T), dim3(GN_THREADS), (size_t)2 * d * sizeof(float), stream, a, Sa, (size_t)stride_a, wa, b, Sb,
+                   (size_t)stride_b, wb, eps, mix, out, d);
+    return kestrel_check_launch("combine_normed");
+}
+
+// ------------------------------------------------------------------------------------------
+// A sublayer's result y (slices, optional bias) is gated by sigmoid(g + g_bias) where a gate product g is
+// given, normalised over the row with the weight w, and added to the residual stream:
+//     residual[t] += (y * sigmoid(g)) / sqrt(mean((y * sigmoid(g))^2) + eps) * w
+// and, where `next_w` is given, the next norm of the stream is made in the same pass:
+//     next_out[t] = residual[t] / sqrt(mean(residual[t]^2) + eps_next) * next_w       (storage type)
+// ------------------------------------------------------------------------------------------
+template <typename TOut>
+__global__ void __launch_bounds__(GN_THREADS)
+add_gated_normed_kernel(float *__restrict__ residual, const float *__restrict__ y, int Sy, size_t stride_y, const float *__restrict__ y_bias,
+                        const float *__restrict__ g, int Sg, size_t stride_g, const float *__restrict__ g_bias, const float *__restrict__ w,
+                        float eps, const float *__restrict__ next_w, float eps_next, TOut *__restrict__ next_out, int d) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float gn_row[];
+    __shared__ float red[GN_THREADS / 32];
+    const int t = blockIdx.x;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += GN_THREADS) {
+        float v = sum_slices(y, Sy, stride_y, (size_t)t * d + i);
+        if (y_bias) v += y_bias[i];
+        if (g) {
+            float z = sum_slices(g, Sg, stride_g, (size_t)t * d + i);
+            if (g_bias) z += g_bias[i];
+            v *= 1.0f / (1.0f + expf(-z));
+        }
+        gn_row[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    const float rn = 1.0f / sqrtf(gn_block_sum(ss, red) / (float)d + eps);
+    float s2 = 0.f;
+    for (int i = threadIdx.x; i < d; i += GN_THREADS) {
+        const float x = residual[(size_t)t * d + i] + gn_row[i] * rn * w[i];
+        residual[(size_t)t * d + i] = x;
+        gn_row[i] = x;
+        s2 = fmaf(x, x, s2);
+    }
+    if (!next_w) return;
+    const float r2 = 1.0f / sqrtf(gn_block_sum(s2, red) / (float)d + eps_next);
+    for (int i = threadIdx.x; i < d; i += GN_THREADS) next_out[(size_t)t * d + i] = from_f32<TOut>(gn_row[i] * r2 * next_w[i]);
+}
+
+KESTREL_API int kestrel_add_gated_normed(float *residual, const float *y, int Sy, long long stride_y, const float *y_bias, const float *g, int Sg,
+                                         long long stride_g, const float *g_bias, const float *w, float eps, const float *next_w, float eps_next,
+                                         void *next_out, int next_dtype, int T, int d, cudaStream_t stream) {
+    if (T == 0) return 0;
+    KESTREL_REQUIRE(T > 0 && d > 0 && Sy > 0 && (!g || Sg > 0) && d <= 12000 && ((next_w == nullptr) == (next_out == nullptr)),
+                    "add_gated_normed: bad arguments T=%d d=%d", T, d);
+    if (next_dtype == KESTREL_F32 || !next_w)
+        kestrel_launch(add_gated_normed_kernel<float>, dim3(T), dim3(GN_THREADS), (size_t)d * sizeof(float), stream, residual, y, Sy, (size_t)stride_y, y_bias,
+                       g, Sg, (size_t)stride_g, g_bias, w, eps, next_w, eps_next, (float *)next_out, d);
+    else if (next_dtype == KESTREL_BF16)
+        kestrel_launch(add_gated_normed_kernel<__nv_bfloat16>, dim3(T), dim3(GN_THREADS), (size_t)d * sizeof(float), stream, residual, y, Sy, (size_t)stride_y,
+                       y_bias, g, Sg, (size_t)stride_g, g_bias, w, eps, next_w, eps_next, (__nv_bfloat16 *)next_out, d);
+    else
+        return kestrel_fail(-2, "add_gated_normed: unknown dtype %d", next_dtype);
+    return kestrel_check_launch("add_gated_normed");
+}
+
+// ------------------------------------------------------------------------------------------
+// x[t] += table[ids[t]]: the embedded tokens added to the stream again (a model that runs some
+// of its layers several times feeds them in before each further pass)
+// ------------------------------------------------------------------------------------------
+template <typename TW>
+__global__ void embed_add_kernel(const TW *__restrict__ table, const int *__restrict__ ids, float *__restrict__ x, int d) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const TW *row = table + (size_t)ids[t] * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) x[(size_t)t * d + i] += to_f32<TW>(row[i]);
+}
+
+KESTREL_API int kestrel_embed_add(const void *table, int dtype, const int *ids, float *x, int T, int d, cudaStream_t stream) {
+    if (T == 0) return 0;
+    KESTREL_REQUIRE(T > 0 && d > 0, "embed_add: bad sizes");
+    if (dtype == KESTREL_F32) kestrel_launch(embed_add_kernel<float>, dim3(T), dim3(256), 0, stream, (const float *)table, ids, x, d);
+    else if (dtype == KESTREL_BF16) kestrel_launch(embed_add_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, (const __nv_bfloat16 *)table, ids, x, d);
+    else return kestrel_fail(-2, "embed_add: unknown dtype %d", dtype);
+    return kestrel_check_launch("embed_add");
+}
+
+// ------------------------------------------------------------------------------------------
+// logits <- logits * scale, then cap * tanh(logits / cap) where cap > 0; in place, float32
+// ------------------------------------------------------------------------------------------
+__global__ void logit_scale_cap_kernel(float *__restrict__ logits, size_t ld, int V, float scale, float cap) {
+    pdl_launch_dependents();
+    pdl_wait();
+    float *row = logits + (size_t)blockIdx.y * ld;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= V) return;
+    float z = row[i] * scale;
+    if (cap > 0.f) z = cap * tanhf(z / cap);
+    row[i] = z;
+}
+
+KESTREL_API int kestrel_logit_scale_cap(float *logits, long long ld, int R, int V, float scale, float cap, cudaStream_t stream) {
+    if (R == 0) return 0;
+    KESTREL_REQUIRE(R > 0 && R <= 65535 && V > 0 && cap >= 0.f, "logit_scale_cap: bad sizes R=%d V=%d", R, V);
+    kestrel_launch(logit_scale_cap_kernel, dim3((V + 255) / 256, R), dim3(256), 0, stream, logits, (size_t)ld, V, scale, cap);
+    return kestrel_check_launch("logit_scale_cap");
+}

@@ -791,6 +791,79 @@ def partial_columns(p: Partials, col0: int, n: int, dtype: torch.dtype) -> torch
     return out
 
 
+COLUMN_ACTS = {None: 0, "none": 0, "relu2": 1, "tanh": 2, "silu": 3}
+
+
+def partial_columns_act(p: Partials, col0: int, n: int, dtype: torch.dtype, act: Optional[str]) -> torch.Tensor:
+    """act(columns [col0, col0 + n) of a product, summed over its slices, plus its bias) in ``dtype``;
+    ``act`` None, "relu2" (the square of relu), "tanh" or "silu"."""
+    if act not in COLUMN_ACTS:
+        raise KernelError(f"partial_columns_act: activation {act!r} is none of {', '.join(str(k) for k in COLUMN_ACTS)}")
+    out = torch.empty((p.tokens, n), dtype=dtype, device=p.data.device)
+    if p.bias is not None and p.bias.shape[0] != p.width:
+        raise KernelError("partial_columns_act: the bias does not fit the product's columns")
+    _check(library().kestrel_partial_columns_act(p.data.data_ptr(), p.slices, p.slice_stride, p.width, int(col0), _p(p.bias), COLUMN_ACTS[act],
+                                                 out.data_ptr(), _code(out, "partial_columns_act.out"), p.tokens, int(n), _stream()))
+    return out
+
+
+def combine_normed(a: Partials, wa: torch.Tensor, b: Partials, wb: torch.Tensor, eps: float, mix: float) -> Partials:
+    """mix * (rmsnorm(a) * wa + rmsnorm(b) * wb) over the rows of two products, as a product of one slice."""
+    _need(wa, "combine_normed.wa", torch.float32, 1)
+    _need(wb, "combine_normed.wb", torch.float32, 1)
+    T, d = a.tokens, a.width
+    if b.tokens != T or b.width != d or wa.shape[0] != d or wb.shape[0] != d or a.bias is not None or b.bias is not None:
+        raise KernelError("combine_normed: shapes differ, or a bias is pending")
+    out = torch.empty((1, T, d), dtype=torch.float32, device=a.data.device)
+    _check(library().kestrel_combine_normed(a.data.data_ptr(), a.slices, a.slice_stride, wa.data_ptr(), b.data.data_ptr(), b.slices, b.slice_stride,
+                                            wb.data_ptr(), float(eps), float(mix), out.data_ptr(), T, d, _stream()))
+    return Partials(out)
+
+
+def add_gated_normed(residual: torch.Tensor, y: Partials, gate: Optional[Partials], weight: torch.Tensor, eps: float,
+                     next_weight: Optional[torch.Tensor] = None, next_eps: float = 0.0, next_out: Optional[torch.Tensor] = None) -> None:
+    """residual += rmsnorm(y * sigmoid(gate)) * weight, y and gate the sums of their slices plus their
+    biases (no gate: y alone); with ``next_weight`` also next_out = rmsnorm(residual) * next_weight."""
+    _need(residual, "add_gated_normed.residual", torch.float32, 2)
+    _need(weight, "add_gated_normed.weight", torch.float32, 1)
+    T, d = residual.shape
+    for p in (y, gate):
+        if p is not None and (p.tokens != T or p.width != d or (p.bias is not None and p.bias.shape[0] != d)):
+            raise KernelError("add_gated_normed: a product does not fit the residual stream")
+    if (next_weight is None) != (next_out is None):
+        raise KernelError("add_gated_normed: the next norm needs its weight and its output")
+    if next_out is not None:
+        _need(next_out, "add_gated_normed.next_out", dims=2)
+        _need(next_weight, "add_gated_normed.next_weight", torch.float32, 1)
+        if next_out.shape != residual.shape or next_weight.shape[0] != d:
+            raise KernelError("add_gated_normed: the next norm's shapes differ")
+    if weight.shape[0] != d:
+        raise KernelError("add_gated_normed: the weight does not fit the row")
+    _check(library().kestrel_add_gated_normed(
+        residual.data_ptr(), y.data.data_ptr(), y.slices, y.slice_stride, _p(y.bias), _p(gate.data) if gate is not None else None,
+        gate.slices if gate is not None else 0, gate.slice_stride if gate is not None else 0, _p(gate.bias) if gate is not None else None,
+        weight.data_ptr(), float(eps), _p(next_weight), float(next_eps), _p(next_out),
+        _code(next_out, "add_gated_normed.next_out") if next_out is not None else F32, T, d, _stream()))
+
+
+def embed_add(table: torch.Tensor, ids: torch.Tensor, x: torch.Tensor) -> None:
+    """x[t] += table[ids[t]] widened to float32."""
+    _need(table, "embed_add.table", dims=2)
+    _need(ids, "embed_add.ids", torch.int32, 1)
+    _need(x, "embed_add.x", torch.float32, 2)
+    if ids.shape[0] != x.shape[0] or table.shape[1] != x.shape[1]:
+        raise KernelError("embed_add: shapes differ")
+    _check(library().kestrel_embed_add(table.data_ptr(), _code(table, "embed_add.table"), ids.data_ptr(), x.data_ptr(), x.shape[0], x.shape[1],
+                                       _stream()))
+
+
+def logit_scale_cap(logits: torch.Tensor, scale: float, cap: float) -> None:
+    """In place: logits * scale, then cap * tanh(. / cap) where cap > 0."""
+    _need(logits, "logit_scale_cap.logits", torch.float32, 2)
+    _check(library().kestrel_logit_scale_cap(logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1], float(scale), float(cap),
+                                             _stream()))
+
+
 # ---- attention without rotation, values of their own size, kept first tokens, an output gate -----
 
 QK_NORM_MODES = {None: 0, False: 0, "none": 0, True: 1, "head": 1, "projection": 2}
@@ -799,13 +872,14 @@ QK_NORM_MODES = {None: 0, False: 0, "none": 0, True: 1, "head": 1, "projection":
 def attn_prepare_ex(qkv: Partials, q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], qk_norm, norm_eps: float,
                     positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor, page_size: int,
                     k_cache: torch.Tensor, v_cache: torch.Tensor, q_out: torch.Tensor, gate_out: Optional[torch.Tensor],
-                    nq: int, nkv: int, hd: int, vd: int, has_kv: bool, v_norm: bool = False) -> None:
+                    nq: int, nkv: int, hd: int, vd: int, has_kv: bool, v_norm: bool = False, rotation=None) -> None:
     """Columns [q | k | v | gate] of a fused product, plus the product's bias where it carries one:
     q and k divided by their root mean square - ``qk_norm`` "head" (or True): per head, times a
     weight [hd] where given; "projection": over all of q's columns at once and all of k's, times
     weights [nq hd] and [nkv hd]; None: left as they are - and v per head if ``v_norm``; q to
     ``q_out``, k and v into the cache pages (absent if ``has_kv`` is False), sigmoid of the gate
-    columns to ``gate_out`` float32 [T, nq]."""
+    columns to ``gate_out`` float32 [T, nq].  With ``rotation`` (a `Rotation` of parts/base.py: frequencies,
+    rotated size, pairing, scale) q and k are turned by position after their norm."""
     _need(q_out, "attn_prepare_ex.q_out", dims=2)
     _need(block_table, "attn_prepare_ex.block_table", torch.int32, 2)
     _need(k_cache, "attn_prepare_ex.k_cache", q_out.dtype, 4)
@@ -828,9 +902,15 @@ def attn_prepare_ex(qkv: Partials, q_norm_w: Optional[torch.Tensor], k_norm_w: O
         raise KernelError("attn_prepare_ex: the cache planes do not fit the heads")
     if gate_out is not None:
         _need(gate_out, "attn_prepare_ex.gate_out", torch.float32, 2)
-    _check(library().kestrel_attn_prepare_normed(
+    inv_freq = rot = rot_mode = None
+    if rotation is not None:
+        inv_freq, rot, rot_mode = rotation.inv_freq, int(rotation.dim), rotation.mode
+        _need(inv_freq, "attn_prepare_ex.inv_freq", torch.float32, 1)
+        if rot <= 0 or rot % 2 or rot > hd or inv_freq.shape[0] < rot // 2:
+            raise KernelError(f"attn_prepare_ex: {rot} rotated dimensions of a head of {hd} with {inv_freq.shape[0]} frequencies")
+    _check(library().kestrel_attn_prepare_rotated(
         qkv.data.data_ptr(), qkv.slices, qkv.slice_stride, qkv.width, _p(qkv.bias), _p(q_norm_w), _p(k_norm_w), mode, 1 if v_norm else 0,
-        float(norm_eps), positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(), block_table.stride(0), int(page_size),
+        float(norm_eps), _p(inv_freq), rot or 0, rot_mode or 0, float(rotation.scale) if rotation is not None else 1.0, positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(), block_table.stride(0), int(page_size),
         k_cache.data_ptr(), v_cache.data_ptr(), q_out.data_ptr(), _p(gate_out), _code(q_out, "attn_prepare_ex.q_out"), T, nq, nkv, hd, vd,
         1 if has_kv else 0, _stream()))
 
@@ -842,28 +922,31 @@ class ScoreOptions:
     """What a layer does to its scores s = q . k * scale and how it weighs keys, all in float32:
     ``softcap`` > 0: s <- softcap tanh(s / softcap); ``r1``, ``r2`` (float32 [heads], both or
     neither): s <- s - r1[h] ln(1 + r2[h] (i - j)) for the key j behind the query i; ``weighting``
-    "softmax", "softmax_sink" (one more term exp(0) in the denominator, without a value) or
-    "sigmoid" (every visible key weighs sigmoid(s + head_bias[h]), nothing is normalised)."""
+    "softmax", "softmax_sink" (one more term in the denominator, without a value: exp(sink[h]) with
+    ``sink`` float32 [heads], exp(0) without it) or "sigmoid" (every visible key weighs
+    sigmoid(s + head_bias[h]), nothing is normalised)."""
 
-    __slots__ = ("softcap", "r1", "r2", "head_bias", "weighting")
+    __slots__ = ("softcap", "r1", "r2", "head_bias", "weighting", "sink")
 
     def __init__(self, softcap: float = 0.0, r1: Optional[torch.Tensor] = None, r2: Optional[torch.Tensor] = None,
-                 head_bias: Optional[torch.Tensor] = None, weighting: str = "softmax"):
+                 head_bias: Optional[torch.Tensor] = None, weighting: str = "softmax", sink: Optional[torch.Tensor] = None):
         if weighting not in WEIGHTINGS:
             raise KernelError(f"weighting '{weighting}' is none of {', '.join(WEIGHTINGS)}")
         if (r1 is None) != (r2 is None):
             raise KernelError("the distance term needs both of its per-head numbers")
         if softcap < 0:
             raise KernelError("a score cap is positive, or 0 for none")
-        self.softcap, self.r1, self.r2, self.head_bias, self.weighting = float(softcap), r1, r2, head_bias, weighting
+        if sink is not None and weighting != "softmax_sink":
+            raise KernelError("numbers for the denominator's extra term belong to the weighting 'softmax_sink'")
+        self.softcap, self.r1, self.r2, self.head_bias, self.weighting, self.sink = float(softcap), r1, r2, head_bias, weighting, sink
 
     def args(self, nq: int):
-        for t, name in ((self.r1, "r1"), (self.r2, "r2"), (self.head_bias, "head_bias")):
+        for t, name in ((self.r1, "r1"), (self.r2, "r2"), (self.head_bias, "head_bias"), (self.sink, "sink")):
             if t is not None:
                 _need(t, f"score.{name}", torch.float32, 1)
                 if t.shape[0] != nq:
                     raise KernelError(f"score.{name}: {t.shape[0]} entries for {nq} heads")
-        return self.softcap, _p(self.r1), _p(self.r2), _p(self.head_bias), WEIGHTINGS[self.weighting]
+        return self.softcap, _p(self.r1), _p(self.r2), _p(self.head_bias), WEIGHTINGS[self.weighting], _p(self.sink)
 
 
 _NO_SCORE = ScoreOptions()
@@ -1085,6 +1168,77 @@ def delta_out(o: torch.Tensor, weight: torch.Tensor, eps: float, gate: Partials,
         raise KernelError("delta_out: shapes differ")
     _check(library().kestrel_delta_out(o.data_ptr(), weight.data_ptr(), float(eps), gate.data.data_ptr(), gate.slices, gate.slice_stride,
                                        out.data_ptr(), _code(out, "delta_out.out"), T, H, dv, _stream()))
+
+
+# ---- linear recurrences with a matrix of state per head ---------------------------------------
+
+def forget_gates(fused: Partials, col_q: int, col_f: int, col_v: int, f_bias: Optional[torch.Tensor], lower: Optional[torch.Tensor],
+                 n: int, nv: int):
+    """(r, w, k, v) float32 for `recurrence_scan` from a fused product's columns: r = silu(q),
+    w = lower + (1 - lower) * sigmoid(f + f_bias), k = 1 - w, v as it is."""
+    T, dev = fused.tokens, fused.data.device
+    if fused.bias is not None:
+        raise KernelError("forget_gates: a bias is pending on the fused product")
+    r, w, k = (torch.empty((T, n), dtype=torch.float32, device=dev) for _ in range(3))
+    v = torch.empty((T, nv), dtype=torch.float32, device=dev)
+    _check(library().kestrel_forget_gates(fused.data.data_ptr(), fused.slices, fused.slice_stride, fused.width, int(col_q), int(col_f), int(col_v),
+                                          _p(f_bias), _p(lower), r.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(), T, int(n), int(nv), _stream()))
+    return r, w, k, v
+
+
+def removal_gates(fused: Partials, col_r: int, col_k: int, col_v: int, col_a: int, a_bias: Optional[torch.Tensor], wz: Partials,
+                  w_bias: Optional[torch.Tensor], decay_rate: float, H: int, d: int):
+    """(r, w, k, v, a, b) float32 for `recurrence_scan` from a fused product's columns and the decay's
+    second product ``wz``: u = k / sqrt(sum k^2 + 1e-6) per head, w = exp(-decay_rate * sigmoid(wz + w_bias)),
+    a = -(sigmoid(rate + a_bias) * u), b = u."""
+    T, dev, n = fused.tokens, fused.data.device, H * d
+    if fused.bias is not None or wz.bias is not None or wz.tokens != T or wz.width != n:
+        raise KernelError("removal_gates: shapes differ, or a bias is pending")
+    r, w, k, v, a, b = (torch.empty((T, n), dtype=torch.float32, device=dev) for _ in range(6))
+    _check(library().kestrel_removal_gates(fused.data.data_ptr(), fused.slices, fused.slice_stride, fused.width, int(col_r), int(col_k), int(col_v),
+                                           int(col_a), _p(a_bias), wz.data.data_ptr(), wz.slices, wz.slice_stride, _p(w_bias), float(decay_rate),
+                                           r.data_ptr(), k.data_ptr(), v.data_ptr(), w.data_ptr(), a.data_ptr(), b.data_ptr(), T, H, d, _stream()))
+    return r, w, k, v, a, b
+
+
+def recurrence_scan(r: torch.Tensor, w: torch.Tensor, k: torch.Tensor, v: torch.Tensor, a: Optional[torch.Tensor], b: Optional[torch.Tensor],
+                    state: torch.Tensor, state_off: int, batch, H: int, d: int, dv: int) -> torch.Tensor:
+    """S <- diag(w) S + a (b^T S) + k v^T, o = S^T r per head over this step's tokens of every request,
+    from and to the requests' state slots (S [H, d, dv] at ``state_off`` floats into a slot); returns
+    o float32 [T, H dv].  ``a`` and ``b`` None: no correction term."""
+    _need(state, "recurrence_scan.state", torch.float32, 2)
+    T = r.shape[0]
+    for t, name, n in ((r, "r", H * d), (w, "w", H * d), (k, "k", H * d), (v, "v", H * dv), (a, "a", H * d), (b, "b", H * d)):
+        if t is not None:
+            _need(t, f"recurrence_scan.{name}", torch.float32, 2)
+            if t.shape != (T, n):
+                raise KernelError(f"recurrence_scan.{name}: shape {tuple(t.shape)}, expected ({T}, {n})")
+    if state_off < 0 or state_off + H * d * dv > state.shape[1]:
+        raise KernelError("recurrence_scan: the state does not fit the slot")
+    out = torch.empty((T, H * dv), dtype=torch.float32, device=r.device)
+    _check(library().kestrel_recurrence_scan(r.data_ptr(), w.data_ptr(), k.data_ptr(), v.data_ptr(), _p(a), _p(b), state.data_ptr(), state.stride(0),
+                                             int(state_off), batch.cu_seqlens.data_ptr(), batch.slots.data_ptr(), out.data_ptr(), batch.num_seqs,
+                                             H, d, dv, _stream()))
+    return out
+
+
+def head_norm_gate(o: torch.Tensor, weight: torch.Tensor, eps: float, gate: Optional[Partials], gate_col0: int, out: torch.Tensor,
+                   H: int, dv: int) -> None:
+    """out = o / sqrt(mean(o^2) + eps) per head, times ``weight`` ([dv]: shared by the heads; [H dv]: one per
+    head), times sigmoid of the columns [gate_col0, gate_col0 + H dv) of ``gate`` where given."""
+    _need(o, "head_norm_gate.o", torch.float32, 2)
+    _need(weight, "head_norm_gate.weight", torch.float32, 1)
+    _need(out, "head_norm_gate.out", dims=2)
+    T = o.shape[0]
+    if o.shape[1] != H * dv or out.shape != o.shape or weight.shape[0] not in (dv, H * dv):
+        raise KernelError("head_norm_gate: shapes differ")
+    if gate is not None and (gate.tokens != T or gate.bias is not None or gate_col0 + H * dv > gate.width):
+        raise KernelError("head_norm_gate: the gate's product does not fit, or carries a bias")
+    w_stride = dv if (weight.shape[0] == H * dv and H > 1) else 0
+    _check(library().kestrel_head_norm_gate(o.data_ptr(), weight.data_ptr(), w_stride, float(eps), _p(gate.data) if gate is not None else None,
+                                            gate.slices if gate is not None else 0, gate.slice_stride if gate is not None else 0,
+                                            gate.width if gate is not None else 0, int(gate_col0), out.data_ptr(), _code(out, "head_norm_gate.out"),
+                                            T, H, dv, _stream()))
 
 
 # ---- routed feed-forward -----------------------------------------------------------------------

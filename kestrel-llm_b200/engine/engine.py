@@ -71,11 +71,11 @@ class Engine:
         memory holds (the weights are loaded already), at most batch_max requests of
         max_model_len tokens; the choice is printed."""
         import sys
-        from ..parts.base import PagedKVSpec
+        from ..parts.base import paged_part
         want = options.batch_max * self.max_model_len
         esize = torch.empty((), dtype=model.dtype).element_size()
-        per_token = sum(sp.kv_heads * (sp.head_dim + (0 if sp.values_are_keys else sp.value_dim)) * esize for sp in model.cache_specs()
-                        if isinstance(sp, PagedKVSpec))
+        per_token = sum(sp.kv_heads * (sp.head_dim + (0 if sp.values_are_keys else sp.value_dim)) * esize for sp in map(paged_part, model.cache_specs())
+                        if sp is not None)
         if per_token == 0:
             return max(1, (want + page - 1) // page)
         free, _total = torch.cuda.mem_get_info(model.device)

@@ -164,6 +164,16 @@ KESTREL_API int kestrel_gelu_table_mul(const float *g, int S, long long slice_st
 KESTREL_API int kestrel_add_normed(float *residual, const float *p, int S, long long slice_stride, const float *w, float eps, int T, int d, kestrel_stream_t stream);
 /* out[t, i] = sum of p's slices at [t, col0 + i], i < n, in the storage type */
 KESTREL_API int kestrel_partial_columns(const float *p, int S, long long slice_stride, int ld, int col0, void *out, int dtype, int T, int n, kestrel_stream_t stream);
+/* the same with the product's bias (NULL: none; indexed like the product's columns) and an activation on the sum: 0 none, 1 relu squared, 2 tanh, 3 silu */
+KESTREL_API int kestrel_partial_columns_act(const float *p, int S, long long slice_stride, int ld, int col0, const float *bias, int act, void *out, int dtype, int T, int n, kestrel_stream_t stream);
+/* out[t] = mix (a / sqrt(mean(a^2) + eps) wa + b / sqrt(mean(b^2) + eps) wb), a and b the sums of two products' slices, float32 */
+KESTREL_API int kestrel_combine_normed(const float *a, int Sa, long long stride_a, const float *wa, const float *b, int Sb, long long stride_b, const float *wb, float eps, float mix, float *out, int T, int d, kestrel_stream_t stream);
+/* v = (sum of y's slices + y_bias) * sigmoid(sum of g's slices + g_bias) (g may be NULL: no gate); residual[t] += v / sqrt(mean(v^2) + eps) w; with next_w also next_out[t] = residual[t] / sqrt(mean(residual[t]^2) + eps_next) next_w in the storage type */
+KESTREL_API int kestrel_add_gated_normed(float *residual, const float *y, int Sy, long long stride_y, const float *y_bias, const float *g, int Sg, long long stride_g, const float *g_bias, const float *w, float eps, const float *next_w, float eps_next, void *next_out, int next_dtype, int T, int d, kestrel_stream_t stream);
+/* x[t] += table[ids[t]] */
+KESTREL_API int kestrel_embed_add(const void *table, int dtype, const int *ids, float *x, int T, int d, kestrel_stream_t stream);
+/* logits <- logits * scale, then cap tanh(logits / cap) where cap > 0; in place */
+KESTREL_API int kestrel_logit_scale_cap(float *logits, long long ld, int R, int V, float scale, float cap, kestrel_stream_t stream);
 
 /* ---- attention without rotation, with values of their own size, kept first tokens and an output gate ---- */
 /* product columns [q: nq hd | k: nkv hd | v: nkv vd | gate: nq]; k, v absent if has_kv = 0, gate if gate_out is NULL; qk_norm: q, k / sqrt(mean(x^2) + eps) per head, times q_norm_w / k_norm_w [hd] where given */
@@ -176,16 +186,18 @@ KESTREL_API int kestrel_attention_window(const void *q, const void *k_cache, con
 
 /* ---- options on the scores and on the weighing of keys (attention_score.cuh); all float32 ----
    softcap > 0: s <- softcap tanh(s / softcap); r1, r2 [nq] (both or neither): s <- s - r1[h] ln(1 + r2[h] (i - j));
-   weighting 0: softmax; 1: softmax with a valueless extra term exp(0) in the denominator; 2: every visible key weighs
-   sigmoid(s + head_bias[h]) (head_bias [nq] or NULL), not normalised over keys */
-KESTREL_API int kestrel_attention_plain_scored(const void *q, const void *k_cache, const void *v_cache, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *out, int dtype, int T, int nq, int nkv, int hd, int vd, int window, int keep_first, const float *gate, float scale, float softcap, const float *r1, const float *r2, const float *head_bias, int weighting, kestrel_stream_t stream);
-KESTREL_API int kestrel_attention_window_scored(const void *q, const void *k_cache, const void *v_cache, void *out, const float *gate, const int *cu_seqlens, const int *kv_lens, const int *block_table, int table_stride, int page_size, int nseq, int max_count, int nq, int nkv, int hd, int vd, int window, int keep_first, float scale, float softcap, const float *r1, const float *r2, const float *head_bias, int weighting, int ksplit, float *scratch, kestrel_stream_t stream);
+   weighting 0: softmax; 1: softmax with a valueless extra term exp(sink[h]) in the denominator (sink [nq], or NULL for
+   exp(0)); 2: every visible key weighs sigmoid(s + head_bias[h]) (head_bias [nq] or NULL), not normalised over keys */
+KESTREL_API int kestrel_attention_plain_scored(const void *q, const void *k_cache, const void *v_cache, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *out, int dtype, int T, int nq, int nkv, int hd, int vd, int window, int keep_first, const float *gate, float scale, float softcap, const float *r1, const float *r2, const float *head_bias, int weighting, const float *sink, kestrel_stream_t stream);
+KESTREL_API int kestrel_attention_window_scored(const void *q, const void *k_cache, const void *v_cache, void *out, const float *gate, const int *cu_seqlens, const int *kv_lens, const int *block_table, int table_stride, int page_size, int nseq, int max_count, int nq, int nkv, int hd, int vd, int window, int keep_first, float scale, float softcap, const float *r1, const float *r2, const float *head_bias, int weighting, const float *sink, int ksplit, float *scratch, kestrel_stream_t stream);
 /* a step of single tokens may cut its key rounds into `ksplit` shares, a CTA each, merged by a second kernel; scratch of kestrel_attention_window_scratch_floats floats */
 KESTREL_API int kestrel_attention_window_splits(int nseq, int max_count, int nq, int nkv, int hd, int vd, int window, int max_kv_len);
 KESTREL_API long long kestrel_attention_window_scratch_floats(int nseq, int max_count, int nq, int nkv, int hd, int vd, int ksplit);
-KESTREL_API int kestrel_attention_tc_scored(const void *q, const void *k_cache, const void *v_cache, void *out, float *part_o, float *part_ml, const int *tile_seq, const int *tile_row0, int tiles, int rows_per_tile, const int *cu_seqlens, const int *kv_lens, const int *block_table, int table_width, int table_stride, int page_size, int cache_pages, int T, int nq, int nkv, int hd, int window, int slices, int slice_len, const int *max_kv_ptr, float scale, float softcap, const float *r1, const float *r2, const float *head_bias, int weighting, kestrel_stream_t stream);
+KESTREL_API int kestrel_attention_tc_scored(const void *q, const void *k_cache, const void *v_cache, void *out, float *part_o, float *part_ml, const int *tile_seq, const int *tile_row0, int tiles, int rows_per_tile, const int *cu_seqlens, const int *kv_lens, const int *block_table, int table_width, int table_stride, int page_size, int cache_pages, int T, int nq, int nkv, int hd, int window, int slices, int slice_len, const int *max_kv_ptr, float scale, float softcap, const float *r1, const float *r2, const float *head_bias, int weighting, const float *sink, kestrel_stream_t stream);
 /* attn_prepare_ex with a bias per product column (NULL: none); qk_norm 0: none, 1: per head (weights [hd] or NULL), 2: over the whole q and the whole k projection (weights [nq hd], [nkv hd]); v_norm: v / sqrt(mean(v^2) + eps) per head */
 KESTREL_API int kestrel_attn_prepare_normed(const float *partial, int S, long long slice_stride, int ld, const float *bias, const float *q_norm_w, const float *k_norm_w, int qk_norm, int v_norm, float norm_eps, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *k_cache, void *v_cache, void *q_out, float *gate_out, int dtype, int T, int nq, int nkv, int hd, int vd, int has_kv, kestrel_stream_t stream);
+/* attn_prepare_normed, then q and k turned by position where inv_freq is given: pair j of a head's first `rot` dimensions by position * inv_freq[j]; rot_mode 0 pairs j with j + rot / 2, 1 pairs 2j with 2j + 1; rot_scale multiplies cos and sin */
+KESTREL_API int kestrel_attn_prepare_rotated(const float *partial, int S, long long slice_stride, int ld, const float *bias, const float *q_norm_w, const float *k_norm_w, int qk_norm, int v_norm, float norm_eps, const float *inv_freq, int rot, int rot_mode, float rot_scale, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *k_cache, void *v_cache, void *q_out, float *gate_out, int dtype, int T, int nq, int nkv, int hd, int vd, int has_kv, kestrel_stream_t stream);
 
 /* ---- attention over cached latents (attention_latent.cu) ---- */
 /* product columns [q latent: q_rank | kv latent: kv_rank | gate: n_gate]: both latents RMS-normed with their weights; the query latent to q_out [T, q_rank], the kv latent into the token's slot of latent_cache [pages, 1, page_size, kv_rank], sigmoid of the gate columns to gate_out [T, n_gate]; kv_out (may be NULL) receives the kv latents as rows [T, kv_rank] too */
@@ -201,6 +213,16 @@ KESTREL_API int kestrel_delta_conv_silu(const float *partial, int S, long long s
 KESTREL_API int kestrel_delta_gates(const float *act, int C, const float *partial, int S, long long slice_stride, int ld, int col_beta, const float *a_part, int Sa, long long a_stride, const float *A_log, const float *dt_bias, float *qn, float *kn, float *decay, float *beta, int T, int H, int G, int d, kestrel_stream_t stream);
 KESTREL_API int kestrel_delta_scan(const float *qn, const float *kn, const float *decay, const float *act, int C, int col_v, const float *beta, float *state, long long state_stride, const int *cu_seqlens, const int *slots, float *out, int nseq, int H, int G, int d, int dv, kestrel_stream_t stream);
 KESTREL_API int kestrel_delta_out(const float *o, const float *w, float eps, const float *g_part, int Sg, long long g_stride, void *out, int dtype, int T, int H, int dv, kestrel_stream_t stream);
+
+/* ---- linear recurrences S_t = diag(w) S + a (b^T S) + k v^T, o = S^T r per head (linear_recurrence.cu); S [H, d, dv] float32 at state_off of the request's state slot ---- */
+/* product columns q, f [n = H d] and v [nv = H dv]: r = silu(q), w = lower + (1 - lower) sigmoid(f + f_bias), k = 1 - w, v as it is; all float32 [T, .] */
+KESTREL_API int kestrel_forget_gates(const float *partial, int S, long long slice_stride, int ld, int col_q, int col_f, int col_v, const float *f_bias, const float *lower, float *r_out, float *w_out, float *k_out, float *v_out, int T, int n, int nv, kestrel_stream_t stream);
+/* product columns r, k, v, rate logits [H d each]; wz a second product [T, H d]: u = k / sqrt(sum k^2 + 1e-6) per head, w = exp(-decay_rate sigmoid(wz + w_bias)), a = -(sigmoid(rate + a_bias) u), b = u */
+KESTREL_API int kestrel_removal_gates(const float *partial, int S, long long slice_stride, int ld, int col_r, int col_k, int col_v, int col_a, const float *a_bias, const float *wz, int Sw, long long w_stride, const float *w_bias, float decay_rate, float *r_out, float *k_out, float *v_out, float *w_out, float *a_out, float *b_out, int T, int H, int d, kestrel_stream_t stream);
+/* r, w, k, a, b [T, H d], v and out [T, H dv], float32; a and b both NULL: no correction */
+KESTREL_API int kestrel_recurrence_scan(const float *r, const float *w, const float *k, const float *v, const float *a, const float *b, float *state, long long state_stride, long long state_off, const int *cu_seqlens, const int *slots, float *out, int nseq, int H, int d, int dv, kestrel_stream_t stream);
+/* out = o / sqrt(mean(o^2) + eps) per head, times w[h w_stride + i] (w_stride 0: one weight [dv] for all heads, dv: one per head), times sigmoid of the gate product's columns g_col0 + h dv + i where g_part is given; storage type */
+KESTREL_API int kestrel_head_norm_gate(const float *o, const float *w, int w_stride, float eps, const float *g_part, int Sg, long long g_stride, int g_ld, int g_col0, void *out, int dtype, int T, int H, int dv, kestrel_stream_t stream);
 
 /* ---- routed feed-forward (moe.cu) ---- */
 KESTREL_API int kestrel_moe_route(const float *z_part, int S, long long slice_stride, const float *bias, int *ids, float *weights, int T, int E, int top, kestrel_stream_t stream);

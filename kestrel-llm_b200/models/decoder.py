@@ -4,7 +4,9 @@ norm and an output head.
 ``order`` is a list of `LayerCall`s.  A call names the block it runs and the cache layer it
 uses; a block may appear in several calls (its weights run twice, each call with a cache
 layer of its own or a shared one), and a call with ``writes_cache=False`` reads a cache layer
-that an earlier call of the same step filled.  The reference runs its layers in a fixed loop
+that an earlier call of the same step filled; a call with ``add_embedding`` adds the embedded tokens
+to the stream once more before its block runs (a model that runs a stretch of its layers several
+times feeds them in at the start of each further pass).  The reference runs its layers in a fixed loop
 (src/model/vllm_safetensors.c:16404-16812); here the loop walks this list.
 """
 from __future__ import annotations
@@ -14,6 +16,7 @@ from typing import List, Optional, Sequence
 
 import torch
 
+from ..csrc import ops
 from ..parts.base import Block, CacheSpec, Norm, Part, PositionEncoding, WeightSlot
 from ..parts.embedding import LMHead, TokenEmbedding
 
@@ -23,6 +26,7 @@ class LayerCall:
     block: int                  # index into DecoderModel.blocks
     cache: int = -1             # cache layer it uses, -1 for none
     writes_cache: bool = True   # False: attends over what an earlier call wrote
+    add_embedding: bool = False  # the embedded tokens are added to the stream once more in front of this call
 
 
 class DecoderModel(Part):
@@ -60,6 +64,9 @@ class DecoderModel(Part):
                 elif c.cache not in seen:
                     raise ValueError(f"cache layer {c.cache} is read before it is written")
         self._cache_owner = owners
+        if any(c.add_embedding for c in self.order) and (embedding_norm is not None or (
+                position is not None and type(position).add_to_embedding is not PositionEncoding.add_to_embedding)):
+            raise ValueError("feeding the embedded tokens in again is built for models whose stream starts as the table's rows alone")
 
     @property
     def graph_safe(self) -> bool:
@@ -98,7 +105,8 @@ class DecoderModel(Part):
         from ..csrc import ops
         pos_ok = (self.position is None or type(self.position).add_to_embedding is PositionEncoding.add_to_embedding) \
             and self.embedding_norm is None
-        blocks_ok = all(getattr(b, "emit", None) is not None and getattr(b, "emits", False) for b in self.blocks)
+        blocks_ok = all(getattr(b, "emit", None) is not None and getattr(b, "emits", False) for b in self.blocks) \
+            and not any(c.add_embedding for c in self.order) and getattr(self.lm_head, "plain", True)
         if not (pos_ok and blocks_ok and all(getattr(p, "emit", None) is not None
                                               for p in (self.embedding, self.final_norm, self.lm_head))):
             return None
@@ -135,6 +143,11 @@ class DecoderModel(Part):
         """Layer calls order[lo:hi] on the residual stream ``x`` and the not yet added ``pending``."""
         for call in self.order[lo:hi]:
             lc = cache.layer(call.cache, call.writes_cache) if call.cache >= 0 else None
+            if call.add_embedding:
+                if pending is not None:         # what the call before left unadded goes in first
+                    ops.add_two(x, pending, None, None)
+                    pending = None
+                self.embedding.add_forward(batch.token_ids, x)
             x, pending = self.blocks[call.block].forward(x, pending, batch, lc)
         return x, pending
 

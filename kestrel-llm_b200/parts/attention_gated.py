@@ -1,5 +1,6 @@
-"""Grouped-query softmax attention without rotation, over a window that keeps the first tokens
-of a request, with values of their own size and a gate on every head's output.
+"""Grouped-query softmax attention over a window that keeps the first tokens of a request, with
+values of their own size and a gate on every head's output; without rotation unless it is given a
+position encoding.
 
 q, k, v and the gate logits are one fused product of the mixer's input h.  q and k are divided by
 their root mean square per head (no weight); score = q . k * scale with ``scale`` a parameter;
@@ -15,8 +16,11 @@ with a weight per column (``qk_norm="projection"``), or none at all (``qk_norm=N
 root mean square per head, cached so (``v_norm``); a cap on the scores, s <- cap * tanh(s / cap)
 (``softcap``); a distance term s <- s - r1[n] * ln(1 + r2[n] * (i - j)) with two numbers per head
 (``distance_bias``); and the way keys are weighed (``weighting``): "softmax", "softmax_sink" (the
-denominator has one more term, exp(0), that carries no value) or "sigmoid" (every visible key
-weighs sigmoid(s + pb[n]), pb a number per head if ``head_bias``; nothing is normalised over keys).
+denominator has one more term that carries no value: exp(0), or exp(sink[n]) with a learned number
+per head if ``head_sink``) or "sigmoid" (every visible key weighs sigmoid(s + pb[n]), pb a number
+per head if ``head_bias``; nothing is normalised over keys).  ``position``: a `PositionEncoding` whose
+`rotary()` turns q and k (after their norm) by position - pairing, rotated size, scale and frequencies
+are its own; ``out_bias``: whether the output projection has a bias (default: as ``bias``).
 
 Kernels: float32 and head sizes that are no multiples of 8 run on the plain kernel; bfloat16 on the
 ``mma.sync`` kernel of `ops.attention_window` (single-token steps share their keys out over CTAs),
@@ -30,7 +34,7 @@ from typing import List, Optional
 import torch
 
 from ..csrc import ops
-from .base import Mixer, PagedKVSpec, WeightSlot
+from .base import Mixer, PagedKVSpec, PositionEncoding, WeightSlot
 from .linear import Linear
 
 
@@ -45,7 +49,8 @@ class GatedWindowAttention(Mixer):
                  head_gate: bool = True, cache_window: Optional[int] = None, cache_keep_first: Optional[int] = None,
                  names=("q", "k", "v", "g", "o"), bias: bool = False, qk_norm: Optional[str] = "head", v_norm: bool = False,
                  softcap: float = 0.0, distance_bias: bool = False, weighting: str = "softmax", head_bias: bool = False,
-                 extra_names=None):
+                 extra_names=None, position: Optional[PositionEncoding] = None, head_sink: bool = False,
+                 out_bias: Optional[bool] = None):
         if heads % kv_heads:
             raise ValueError(f"{heads} query heads are not a multiple of {kv_heads} kv heads")
         if max(head_dim, v_head_dim) > 256:
@@ -61,7 +66,10 @@ class GatedWindowAttention(Mixer):
         self.q_cols = heads * head_dim
         self.kv_cols = kv_heads * (head_dim + v_head_dim) if own_kv else 0
         self.proj = Linear(width, self.q_cols + self.kv_cols + (heads if head_gate else 0), dtype, device, bias=bias)
-        self.out = Linear(heads * v_head_dim, width, dtype, device, bias=bias)
+        self.out = Linear(heads * v_head_dim, width, dtype, device, bias=bias if out_bias is None else bool(out_bias))
+        self.rotation = position.rotary() if position is not None else None
+        if self.rotation is not None and self.rotation.dim > head_dim:
+            raise ValueError(f"{self.rotation.dim} rotated dimensions exceed the head size {head_dim}")
         if bias and head_gate and self.proj.bias.device.type != "meta":
             self.proj.bias[self.q_cols + self.kv_cols:].zero_()           # the gate logits have no bias
         if qk_norm not in (None, "head", "projection"):
@@ -76,10 +84,14 @@ class GatedWindowAttention(Mixer):
         self.pb = torch.empty((heads,), **f32) if head_bias else None
         if head_bias and weighting != "sigmoid":
             raise ValueError("a number per head added to the scores changes nothing under a softmax; it belongs to sigmoid weights")
-        self.score = ops.ScoreOptions(softcap, self.r1, self.r2, self.pb, weighting)
+        if head_sink and weighting != "softmax_sink":
+            raise ValueError("a learned number per head for the denominator's extra term belongs to the weighting 'softmax_sink'")
+        self.sink = torch.empty((heads,), **f32) if head_sink else None
+        self.score = ops.ScoreOptions(softcap, self.r1, self.r2, self.pb, weighting, self.sink)
         self._scored = bool(softcap) or distance_bias or weighting != "softmax"
         # checkpoint names of what the options add, after the projections' own names
-        self.extra_names = dict(bias=".b", q_norm=names[0] + ".norm", k_norm=names[1] + ".norm", r1="r1", r2="r2", head_bias="pb")
+        self.extra_names = dict(bias=".b", q_norm=names[0] + ".norm", k_norm=names[1] + ".norm", r1="r1", r2="r2", head_bias="pb",
+                                sink="sink")
         self.extra_names.update(extra_names or {})
 
     def cache_spec(self) -> PagedKVSpec:
@@ -103,6 +115,7 @@ class GatedWindowAttention(Mixer):
                 k_end = self.q_cols + self.kv_heads * self.head_dim
                 slots += [WeightSlot(p + nk + x["bias"], b[self.q_cols:k_end], "bias"),
                           WeightSlot(p + nv + x["bias"], b[k_end:self.q_cols + self.kv_cols], "bias")]
+        if self.out.bias is not None:
             slots.append(WeightSlot(p + no + x["bias"], self.out.bias, "bias"))
         if self.q_norm_w is not None:
             slots.append(WeightSlot(p + x["q_norm"], self.q_norm_w, "norm"))
@@ -112,6 +125,8 @@ class GatedWindowAttention(Mixer):
             slots += [WeightSlot(p + x["r1"], self.r1, "positive"), WeightSlot(p + x["r2"], self.r2, "positive")]
         if self.pb is not None:
             slots.append(WeightSlot(p + x["head_bias"], self.pb, "bias"))
+        if self.sink is not None:
+            slots.append(WeightSlot(p + x["sink"], self.sink, "bias"))
         return slots
 
     def forward(self, x: torch.Tensor, batch, cache, residual: Optional[torch.Tensor] = None) -> Optional[ops.Partials]:
@@ -124,7 +139,7 @@ class GatedWindowAttention(Mixer):
         table = batch.block_table(cache.group)
         ops.attn_prepare_ex(fused, self.q_norm_w, self.k_norm_w, self.qk_norm, self.norm_eps, batch.positions, batch.seq_of_token, table,
                             cache.page_size, cache.k, cache.v, q, gate, self.heads, self.kv_heads, self.head_dim, self.v_head_dim,
-                            self.own_kv, v_norm=self.v_norm)
+                            self.own_kv, v_norm=self.v_norm, rotation=self.rotation)
         score = self.score if self._scored else None
         a = torch.empty((T, self.heads * self.v_head_dim), dtype=self.dtype, device=x.device)
         G = self.heads // self.kv_heads

@@ -26,7 +26,7 @@ class WeightSlot:
 
     ``dest`` may be a slice of a larger fused tensor (rows of a fused QKV matrix).  ``init`` is
     the distribution used by the random-weights mode: "linear" N(0, 0.02), "norm"
-    1 + N(0, 0.02), "bias" N(0, 0.02), "positive" |N(0, 0.02)|."""
+    1 + N(0, 0.02), "bias" N(0, 0.02), "positive" |N(0, 0.02)|, "unit" uniform in [0, 1)."""
     name: str
     dest: torch.Tensor
     init: str = "linear"
@@ -58,7 +58,29 @@ class FixedStateSpec:
     dtype: torch.dtype = torch.float32
 
 
-CacheSpec = Union[PagedKVSpec, FixedStateSpec, None]
+@dataclass(frozen=True)
+class CombinedSpec:
+    """Pages of keys and values AND a state slot in one cache layer: a mixer made of two that run
+    side by side, one attending over the cache, one carrying a recurrent state."""
+    paged: PagedKVSpec
+    state: FixedStateSpec
+
+
+CacheSpec = Union[PagedKVSpec, FixedStateSpec, CombinedSpec, None]
+
+
+def paged_part(spec) -> Optional[PagedKVSpec]:
+    """What a cache layer keeps in pages, if anything."""
+    if isinstance(spec, CombinedSpec):
+        return spec.paged
+    return spec if isinstance(spec, PagedKVSpec) else None
+
+
+def state_part(spec) -> Optional[FixedStateSpec]:
+    """What a cache layer keeps per state slot, if anything."""
+    if isinstance(spec, CombinedSpec):
+        return spec.state
+    return spec if isinstance(spec, FixedStateSpec) else None
 
 
 class Part:

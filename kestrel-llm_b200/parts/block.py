@@ -13,7 +13,10 @@ from typing import List, Optional
 
 import torch
 
+from ..csrc import ops
 from .base import Block, FeedForward, Mixer, Norm, WeightSlot
+from .linear import Linear
+from .norm import RMSNorm
 
 
 class PreNormBlock(Block):
@@ -79,4 +82,52 @@ class ParallelBlock(Block):
         x = torch.empty(residual.shape, dtype=self.dtype, device=residual.device)
         ops.add_two(residual, a, f, x)
         self.side.add_forward(residual, x, batch)
+        return residual, None
+
+
+class SandwichBlock(Block):
+    """A norm in front of each sublayer and another on its result, which may be gated first:
+
+        h = norm1(x);  x += norm1b(mixer(h) * sigmoid(W_g1 h + b_g1))
+        h = norm2(x);  x += norm2b(ffn(h)   * sigmoid(W_g2 h + b_g2))
+
+    (``gate1`` / ``gate2`` None: no gate on that sublayer; ``ffn`` None: the first line alone.)  A
+    sublayer's gate, second norm and add are one kernel, which also makes the norm that follows
+    inside the block; the block adds into the stream itself and hands nothing on."""
+
+    def __init__(self, norm1: RMSNorm, mixer: Mixer, norm1b: RMSNorm, gate1: Optional[Linear], norm2: Optional[RMSNorm],
+                 ffn: Optional[FeedForward], norm2b: Optional[RMSNorm], gate2: Optional[Linear], dtype: torch.dtype, prefix: str,
+                 gate_names=("rg1", "rg2")):
+        if len({norm2 is None, ffn is None, norm2b is None}) != 1:
+            raise ValueError("the feed-forward comes with both of its norms or not at all")
+        if ffn is None and gate2 is not None:
+            raise ValueError("a gate for a feed-forward that is not there")
+        self.norm1, self.mixer, self.norm1b, self.gate1 = norm1, mixer, norm1b, gate1
+        self.norm2, self.ffn, self.norm2b, self.gate2 = norm2, ffn, norm2b, gate2
+        self.dtype, self.prefix, self.gate_names = dtype, prefix, gate_names
+
+    def parts(self):
+        return [p for p in (self.norm1, self.mixer, self.norm1b, self.norm2, self.ffn, self.norm2b) if p is not None]
+
+    def weight_slots(self) -> List[WeightSlot]:
+        slots = [s for p in self.parts() for s in p.weight_slots()]
+        for gate, name in zip((self.gate1, self.gate2), self.gate_names):
+            if gate is not None:
+                slots.append(WeightSlot(self.prefix + name, gate.weight))
+                if gate.bias is not None:
+                    slots.append(WeightSlot(self.prefix + name + ".b", gate.bias, "bias"))
+        return slots
+
+    def forward(self, residual: torch.Tensor, pending, batch, cache):
+        h = self.norm1.add_forward(residual, pending, self.dtype)
+        y = self.mixer.forward(h, batch, cache)
+        g = self.gate1.forward(h) if self.gate1 is not None else None
+        if self.ffn is None:
+            ops.add_gated_normed(residual, y, g, self.norm1b.weight, self.norm1b.eps)
+            return residual, None
+        h = torch.empty(residual.shape, dtype=self.dtype, device=residual.device)
+        ops.add_gated_normed(residual, y, g, self.norm1b.weight, self.norm1b.eps, self.norm2.weight, self.norm2.eps, h)
+        z = self.ffn.forward(h, batch)
+        g = self.gate2.forward(h) if self.gate2 is not None else None
+        ops.add_gated_normed(residual, z, g, self.norm2b.weight, self.norm2b.eps)
         return residual, None

@@ -30,17 +30,26 @@ class TokenEmbedding(Part):
         ops.embed(self.weight, token_ids, out)
         return out
 
+    def add_forward(self, token_ids: torch.Tensor, x: torch.Tensor) -> None:
+        """x += E[token]: the embedded tokens fed into the stream once more."""
+        ops.embed_add(self.weight, token_ids, x)
+
     def emit(self, prog) -> int:
         return prog.embed(self.weight)
 
 
 class LMHead(Part):
+    """``scale`` multiplies the logits; ``softcap`` > 0 then bounds them, cap * tanh(logits / cap)."""
     graph_safe = True
 
     def __init__(self, vocab: int, width: int, dtype: torch.dtype, device, weight_name: str,
-                 tied_to: Optional[TokenEmbedding] = None):
+                 tied_to: Optional[TokenEmbedding] = None, scale: float = 1.0, softcap: float = 0.0):
         self.vocab, self.width = vocab, width
         self.weight_name = weight_name
+        self.scale, self.softcap = float(scale), float(softcap)
+        if self.softcap < 0:
+            raise ValueError("a cap on the logits is positive, or 0 for none")
+        self.plain = self.scale == 1.0 and self.softcap == 0.0     # the product alone: what a step program's output head does
         self.tied = tied_to is not None
         self.weight = tied_to.weight if tied_to is not None else \
             torch.empty((vocab, width), dtype=dtype, device=device)
@@ -52,7 +61,10 @@ class LMHead(Part):
         """x [R, width] -> float32 logits [R, vocab].  The product is not split over K (a split
         product returns slices that a consumer kernel sums; the logits have no such consumer)."""
         logits = torch.empty((1, x.shape[0], self.vocab), dtype=torch.float32, device=x.device)
-        return ops.linear(x, self.weight, logits, weights_static=True)[0]
+        logits = ops.linear(x, self.weight, logits, weights_static=True)[0]
+        if not self.plain:
+            ops.logit_scale_cap(logits, self.scale, self.softcap)
+        return logits
 
     def emit(self, prog, x: int) -> None:
         prog.logits(x, self.weight)

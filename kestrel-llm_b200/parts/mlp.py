@@ -38,3 +38,25 @@ class GatedMLP(FeedForward):
     def emit(self, prog, x: int, residual: Optional[int]) -> int:
         act = prog.gate_up_swiglu(x, self.gate_up.weight, self.intermediate)
         return self.down.emit(prog, act, residual=residual, phase="down")
+
+
+class DenseMLP(FeedForward):
+    """Feed-forward without a gate: y = W_down act(W_up x), ``activation`` "relu2" (the square of
+    relu), "silu" or "tanh"."""
+    graph_safe = True
+
+    def __init__(self, width: int, intermediate: int, dtype: torch.dtype, device, prefix: str, activation: str = "relu2",
+                 names=("up", "down")):
+        if activation not in ("relu2", "silu", "tanh"):
+            raise ValueError(f"activation '{activation}' has no kernel; one of 'relu2', 'silu', 'tanh'")
+        self.width, self.intermediate, self.activation = width, intermediate, activation
+        self.prefix, self.names, self.dtype = prefix, names, dtype
+        self.up = Linear(width, intermediate, dtype, device)
+        self.down = Linear(intermediate, width, dtype, device)
+
+    def weight_slots(self) -> List[WeightSlot]:
+        return [WeightSlot(self.prefix + self.names[0], self.up.weight), WeightSlot(self.prefix + self.names[1], self.down.weight)]
+
+    def forward(self, x: torch.Tensor, batch) -> ops.Partials:
+        act = ops.partial_columns_act(self.up.forward(x), 0, self.intermediate, self.dtype, self.activation)
+        return self.down.forward(act)

@@ -4,10 +4,13 @@ half = rot/2; f_j = 1/theta^(j/half); angle = (float)pos * f_j; dimension j pair
 j + half (reference: st.c:8937-8948 for the frequencies, st.c:8963-8989 for the pairing).  The
 frequencies are made once on the host in float32 and kept on the device; angles, cos and sin
 are computed in float32 inside the kernel that rotates (`ops.attn_prepare`).  ``rotary_dim``
-below the head size rotates only the first dimensions of a head; Qwen3 rotates all.
+below the head size rotates only the first dimensions of a head; Qwen3 rotates all.  A
+`FrequencyScaling` stretches the long wavelengths.
 """
 from __future__ import annotations
 
+import math
+from dataclasses import dataclass
 from typing import Optional, Tuple
 
 import numpy as np
@@ -16,21 +19,45 @@ import torch
 from .base import PositionEncoding, Rotation
 
 
+@dataclass(frozen=True)
+class FrequencyScaling:
+    """Stretching of a rotary encoding's long wavelengths for contexts beyond the ``original`` one, by
+    bands of the wavelength l = 2 pi / f: l < original / high keeps f; l > original / low takes
+    f / factor; between them f is blended, (1 - s) f / factor + s f with
+    s = (original / l - low) / (high - low)."""
+    factor: float
+    low: float
+    high: float
+    original: float
+
+    def apply(self, freq: np.ndarray) -> np.ndarray:
+        f = np.asarray(freq, dtype=np.float64)
+        wave = 2.0 * math.pi / f
+        s = (self.original / wave - self.low) / (self.high - self.low)
+        blended = (1.0 - s) * f / self.factor + s * f
+        return np.where(wave < self.original / self.high, f, np.where(wave > self.original / self.low, f / self.factor, blended))
+
+
 class RotaryHalf(PositionEncoding):
     graph_safe = True
 
     pairing = "half"
 
-    def __init__(self, head_dim: int, theta: float, device, rotary_dim: Optional[int] = None, scale: float = 1.0):
+    def __init__(self, head_dim: int, theta: float, device, rotary_dim: Optional[int] = None, scale: float = 1.0,
+                 scaling: Optional[FrequencyScaling] = None):
         rot = head_dim if rotary_dim is None else rotary_dim
         if rot % 2 or rot <= 0 or rot > head_dim:
             raise ValueError(f"rotary size {rot} must be even and at most the head size {head_dim}")
         self.rotary_dim = rot
         self.theta = float(theta)
         self.scale = float(scale)
+        self.scaling = scaling
         half = rot // 2
-        j = np.arange(half, dtype=np.float32)
-        inv = (np.float32(1.0) / np.power(np.float32(theta), j / np.float32(half), dtype=np.float32))
+        if scaling is None:
+            j = np.arange(half, dtype=np.float32)
+            inv = (np.float32(1.0) / np.power(np.float32(theta), j / np.float32(half), dtype=np.float32))
+        else:       # the bands are decided on the frequencies in float64; the kernel gets them rounded to float32
+            inv = scaling.apply(np.power(float(theta), -np.arange(half, dtype=np.float64) / half))
         self.inv_freq = torch.from_numpy(inv.astype(np.float32)).to(device)
 
     def rotary(self) -> Rotation:

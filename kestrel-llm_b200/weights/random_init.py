@@ -2,7 +2,7 @@
 in place on its device.
 
 Distributions: matrices and embeddings N(0, 0.02), norm weights 1 + N(0, 0.02), biases
-N(0, 0.02).  The reference's own synthetic checkpoint (vqf_convert/test/mk_synth.py:11-37)
+N(0, 0.02), lower bounds of gates uniform in [0, 1).  The reference's own synthetic checkpoint (vqf_convert/test/mk_synth.py:11-37)
 draws uniform values from an LCG; the normal draws here keep activations in the range real
 checkpoints have.  A tensor's values depend on (seed, tensor name) only, so the folder is the
 same on every machine.
@@ -35,6 +35,8 @@ def _draw(shape, init: str, gen: torch.Generator) -> torch.Tensor:
         t += 1.0
     elif init == "positive":
         t.abs_()
+    elif init == "unit":
+        t.uniform_(0.0, 1.0, generator=gen)
     return t
 
 
@@ -74,6 +76,8 @@ def fill_random_(model, seed: int) -> None:
                     tmp += 1.0
                 elif slot.init == "positive":
                     tmp.abs_()
+                elif slot.init == "unit":
+                    tmp.uniform_(0.0, 1.0, generator=gen)
                 slot.dest.copy_(tmp)
             else:
                 rows = slot.dest.shape[0]
