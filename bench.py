@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
     python bench.py --workload mix14b | 32b
-    python bench.py --workload zidivik | tidavik [--size a|b]
+    python bench.py --workload zidivik | tidavik | toredra [--size a|b]
 
 Default run (the headline): decode tokens a second at batch 8, at batch 1 and 64, prefill of
 2,048 tokens, and the same decode through the Python entry point with host tokens in and out.
@@ -32,6 +32,11 @@ which switch the overlap of neighbours off: compare shares).
 window attention with a softmax that has one more term, attention over cached latents; dense gated
 feed-forward) the same way, beside the Qwen3 dense decoder of equal width, heads, depth, feed-forward
 and window.
+
+`--workload toredra`: the Toredra decoder (rotary attention whose softmax has a learned term per head beside a
+forget-gate recurrence, a generalised delta rule, gated and twice-normed sublayers, an ungated feed-forward with
+the square of relu) the same way, beside the Qwen3 dense decoder of equal width, heads, depth, vocabulary and
+feed-forward weights.
 
 Timing: CUDA events on the launching stream around exactly K steps after W warm-up steps, with
 a synchronize on both sides.  Every step streams all weights (15 GB) and the live requests'
@@ -296,11 +301,33 @@ def tidavik_raw(z):
     return {"architecture": "Tidavik", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "max_positions": 8192, "layers": layers}
 
 
+TOREDRA_SIZES = {
+    # width, attention heads / kv heads x head sizes, rotated dimensions, recurrence heads x key / value size, delta heads x size, rank of
+    # the decay's projection, feed-forward (two matrices: as many weights as a gated one of two thirds the size), vocab
+    "a": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, rot=64, r_heads=16, r_dim=64, r_vdim=128, d_heads=16, d_dim=128, rank=64,
+              ff=9216, vocab=32000),
+    "b": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, rot=64, r_heads=32, r_dim=64, r_vdim=128, d_heads=32, d_dim=128, rank=128,
+              ff=18432, vocab=64000),
+}
+
+
+def toredra_raw(z):
+    par = {"left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5,
+                    "rot": {"dims": z["rot"], "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}},
+           "right": {"heads": z["r_heads"], "dim": z["r_dim"], "vdim": z["r_vdim"]}}
+    dlt = {"heads": z["d_heads"], "dim": z["d_dim"], "decay_rank": z["rank"]}
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    layers = [{"type": "parallel", "mixer": par, "mlp": mlp}, {"type": "general_delta", "mixer": dlt, "mlp": mlp},
+              {"type": "general_delta", "mixer": dlt, "mlp": mlp}, {"type": "parallel", "mixer": par, "mlp": mlp}]
+    return {"architecture": "Toredra", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "max_positions": 8192,
+            "logit_scale": 0.5, "logit_softcap": 30.0, "layers": layers}
+
+
 def run_zidivik(args) -> int:
-    """Prefill and decode of the Zidivik or the Tidavik decoder at real layer sizes, beside the Qwen3 dense decoder of equal size."""
+    """Prefill and decode of the Zidivik, the Tidavik or the Toredra decoder at real layer sizes, beside the Qwen3 dense decoder of equal size."""
     import numpy as np
     import torch
-    from kestrel_llm_b200.config import EngineOptions, Qwen3Config, TidavikConfig, ZidivikConfig
+    from kestrel_llm_b200.config import EngineOptions, Qwen3Config, TidavikConfig, ToredraConfig, ZidivikConfig
     from kestrel_llm_b200.config.registry import resolve_architecture
     from kestrel_llm_b200.csrc import ops
     from kestrel_llm_b200.engine import Engine, Entry
@@ -308,8 +335,8 @@ def run_zidivik(args) -> int:
 
     dev = "cuda:0"
     torch.cuda.set_device(0)
-    tidavik = args.workload == "tidavik"
-    z = (TIDAVIK_SIZES if tidavik else ZIDIVIK_SIZES)[args.size]
+    tidavik, toredra = args.workload == "tidavik", args.workload == "toredra"
+    z = (TOREDRA_SIZES if toredra else TIDAVIK_SIZES if tidavik else ZIDIVIK_SIZES)[args.size]
     T, B, CTX = args.prefill_tokens, args.batch, 2048
     W, K = max(3, args.warmup), max(1, min(args.steps, 32))
     pk = peaks()
@@ -317,7 +344,9 @@ def run_zidivik(args) -> int:
     rng = np.random.default_rng(0)
     timed_names = ["linear", "add_rmsnorm", "attn_prepare", "attn_prepare_ex", "attention", "attention_plain_ex", "attention_window", "qkv_prepare_fused",
                    "gate_up_swiglu", "moe_route", "moe_experts", "delta_conv_silu", "delta_gates", "delta_scan", "delta_out", "partial_columns",
-                   "add_two", "gelu_table_mul", "add_normed", "embed", "add_sinusoid", "linear_add_into", "latent_prepare", "head_gemm", "attention_tc"]
+                   "add_two", "gelu_table_mul", "add_normed", "embed", "add_sinusoid", "linear_add_into", "latent_prepare", "head_gemm", "attention_tc",
+                   "forget_gates", "removal_gates", "recurrence_scan", "head_norm_gate", "combine_normed", "add_gated_normed", "partial_columns_act",
+                   "embed_add", "logit_scale_cap", "linear_act"]
 
     def measure(cfg, label):
         model = resolve_architecture(cfg.architecture).build(cfg, torch.bfloat16, dev)
@@ -327,6 +356,11 @@ def run_zidivik(args) -> int:
             if hasattr(m, "dt_bias"):
                 m.dt_bias.normal_(-1.0, 1.0)
                 m.A_log.normal_(-0.5, 0.5)
+            for r in (m, getattr(m, "right", None)):        # forget gates and decays that keep a state for hundreds of tokens
+                if hasattr(r, "f_bias"):
+                    r.f_bias.normal_(2.0, 1.0)
+                if hasattr(r, "w0"):
+                    r.w0.normal_(-1.0, 1.0)
         opts = EngineOptions(dtype="bfloat16", page_size=args.page_size, batch_max=B + 1, max_model_len=CTX + T + 64,
                              max_tokens=B * (CTX + 128) + T + 64, max_step_tokens=max(T, B), prefill_batch=T)
         engine = Engine(model, opts)
@@ -403,6 +437,8 @@ def run_zidivik(args) -> int:
             graphs, engine.graphs = engine.graphs, None
             runner, engine.runner = engine.runner, None        # the parts' forward methods from Python: the same kernels
             for what, fn in (("prefill", prefill), ("decode", decode)):
+                fn()                                 # once untimed: what this walk does for the first time (tensor maps, attributes)
+                torch.cuda.synchronize()
                 acc.clear()
                 fn()
                 torch.cuda.synchronize()
@@ -419,18 +455,43 @@ def run_zidivik(args) -> int:
                 "decode_batch": B, "decode_context": CTX, "decode_ms": round(1000 * dec, 4), "decode_tok_s": round(B / dec, 1),
                 "launches_per_decode_step": int(launches), "device_us_per_operation": split}
 
-    raw = tidavik_raw(z) if tidavik else zidivik_raw(z)
-    zc = (TidavikConfig if tidavik else ZidivikConfig).from_dict(raw)
+    raw = toredra_raw(z) if toredra else tidavik_raw(z) if tidavik else zidivik_raw(z)
+    zc = (ToredraConfig if toredra else TidavikConfig if tidavik else ZidivikConfig).from_dict(raw)
     L = len(raw["layers"])
     dense_raw = dict(QWEN3_8B, num_hidden_layers=L, hidden_size=z["width"], num_attention_heads=z["heads"],
-                     num_key_value_heads=z["kv_heads"], head_dim=z["dim"], intermediate_size=z["ff"] if tidavik else z["top"] * z["ff"],
+                     num_key_value_heads=z["kv_heads"], head_dim=z["dim"],
+                     intermediate_size=z["ff"] * 2 // 3 if toredra else z["ff"] if tidavik else z["top"] * z["ff"],
                      vocab_size=z["vocab"], max_position_embeddings=8192)
     if tidavik:                              # the dense model's layers look through the same window
         dense_raw.update(sliding_window=z["window"], use_sliding_window=True, layer_types=["sliding_attention"] * L)
     qc = Qwen3Config.from_dict(dense_raw)
-    ours = measure(zc, "Tidavik" if tidavik else "Zidivik")
+    ours = measure(zc, "Toredra" if toredra else "Tidavik" if tidavik else "Zidivik")
     dense = measure(qc, "Qwen3 dense, equal size" + (" and window" if tidavik else ""))
     clocks.close()
+    if toredra:
+        D, H, G, d, dv, ff = z["width"], z["heads"], z["kv_heads"], z["dim"], z["vdim"], z["ff"]
+        rn, rv, dn = z["r_heads"] * z["r_dim"], z["r_heads"] * z["r_vdim"], z["d_heads"] * z["d_dim"]
+        par_w = D * (H * d + G * (d + dv)) + H * dv * D + D * (2 * rn + rv) + rv * D
+        dlt_w = D * (5 * dn + z["rank"]) + z["rank"] * dn + dn * D
+        n_par = sum(1 for l in raw["layers"] if l["type"] == "parallel")
+        weights = n_par * par_w + (L - n_par) * dlt_w + L * (2 * ff * D + 2 * D * D) + z["vocab"] * D
+        # products, causal attention (half of the T x T scores), and the scans' three (delta rule: five) passes over each head's state a token
+        flops_prefill = 2.0 * T * (weights - z["vocab"] * D) + n_par * 2.0 * H * (d + dv) * T * T / 2 + \
+            T * (n_par * 6.0 * rn * z["r_vdim"] + (L - n_par) * 10.0 * dn * z["d_dim"])
+        state_bytes = 4.0 * B * (n_par * rn * z["r_vdim"] + (L - n_par) * dn * z["d_dim"]) * 2        # read and written every decode step
+        cache_bytes = 2.0 * B * CTX * n_par * G * (d + dv)
+        rec = {"metric": f"Toredra prefill tokens/s at size {args.size}, bf16, beside Qwen3 dense of equal size", "value": ours["prefill_tok_s"],
+               "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ours["prefill_ms"], "higher_is_better": True,
+               "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "impl": "ours", "workload": "toredra",
+               "data": "synthetic: random weights, uniform random token ids, cache of the context filled with random values",
+               "config": dict(z, layers=[l["type"] for l in raw["layers"]], page_size=args.page_size, peaks=pk["source"], parallelism="single GPU"),
+               "toredra": ours, "dense": dense,
+               "ratio_to_dense": {"prefill": round(ours["prefill_tok_s"] / dense["prefill_tok_s"], 3), "decode": round(ours["decode_tok_s"] / dense["decode_tok_s"], 3)},
+               "prefill_flops_frac_of_peak": round(flops_prefill / (ours["prefill_ms"] / 1000.0) / (pk["bf16_tflops"] * 1e12), 4),
+               "decode_bytes_frac_of_hbm": round((2.0 * weights + state_bytes + cache_bytes) / (ours["decode_ms"] / 1000.0) / (pk["hbm_gbs"] * 1e9), 4),
+               "gpu_launches": ours["launches_per_decode_step"] * K, "clocks": clocks.summary()}
+        print(json.dumps(rec))
+        return 0
     if tidavik:
         D, H, G, d, dv, ff = z["width"], z["heads"], z["kv_heads"], z["dim"], z["vdim"], z["ff"]
         grouped_w = D * (H * d + G * (d + dv)) + H * dv * D
@@ -483,10 +544,10 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (default 16)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length at which the decode steps end (default 4096)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="tokens of the prefill step (default 2048)")
-    ap.add_argument("--workload", default="decode8b", choices=["decode8b", "mix14b", "32b", "zidivik", "tidavik"],
-                    help="decode8b: the headline run; mix14b / 32b: whole workloads through the scheduler; zidivik / tidavik: that decoder "
+    ap.add_argument("--workload", default="decode8b", choices=["decode8b", "mix14b", "32b", "zidivik", "tidavik", "toredra"],
+                    help="decode8b: the headline run; mix14b / 32b: whole workloads through the scheduler; zidivik / tidavik / toredra: that decoder "
                          "at real layer sizes beside Qwen3 dense of equal size")
-    ap.add_argument("--size", default="a", choices=sorted(ZIDIVIK_SIZES), help="layer sizes of --workload zidivik / tidavik")
+    ap.add_argument("--size", default="a", choices=sorted(ZIDIVIK_SIZES), help="layer sizes of --workload zidivik / tidavik / toredra")
     ap.add_argument("--requests", type=int, default=0, help="requests of a workload (0: 32 for mix14b, 16 for 32b)")
     ap.add_argument("--generate", type=int, default=0, help="tokens to generate per request of a workload (0: 256 / 128)")
     ap.add_argument("--step-tokens", type=int, default=2048,
@@ -498,7 +559,7 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py: this engine runs on ONE GPU; --gpus {args.gpus} is not supported (no multi-GPU path exists)")
         return 2
-    if args.workload in ("zidivik", "tidavik"):
+    if args.workload in ("zidivik", "tidavik", "toredra"):
         return run_zidivik(args)
     if args.workload != "decode8b":
         return run_workload(args)

@@ -58,6 +58,22 @@ static inline cudaError_t kestrel_launch(void (*kernel)(KArgs...), dim3 grid, di
     return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
+// Dynamic shared memory to ask for so that the block scheduler spreads a grid of few, long-running
+// CTAs evenly over the SMs.  A kernel launched as a programmatic dependent gets its CTAs placed
+// while the predecessor's last blocks still hold most SMs: the scheduler fills the first SMs that
+// free up with as many CTAs as fit, so a latency-bound scan of 128 small CTAs ends up three to an
+// SM on a third of the chip and runs at half speed.  Asking for 1/n of an SM's shared memory, with
+// n = ceil(ctas / SMs), caps every SM at the share an even spread gives it.  `need` is what the
+// kernel uses; the result is never smaller.  (228 KB an SM, 1 KB of it reserved per resident CTA.)
+#define KESTREL_SMEM_MAX_DYNAMIC (227 * 1024)
+static inline size_t kestrel_spread_smem(long ctas, size_t need) {
+    const long per_sm = (ctas + 147) / 148;
+    if (per_sm > 32) return need;
+    size_t want = ((size_t)(228 * 1024) / (size_t)per_sm - 1024) & ~(size_t)127;
+    if (want > KESTREL_SMEM_MAX_DYNAMIC) want = KESTREL_SMEM_MAX_DYNAMIC;
+    return want > need ? want : need;
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

@@ -280,15 +280,16 @@ KESTREL_API int kestrel_delta_scan(const float *qn, const float *kn, const float
     KESTREL_REQUIRE(H <= 65535 && nseq <= 65535, "delta_scan: grid too large");
     dim3 grid((dv + DR_COLS - 1) / DR_COLS, H, nseq);
 #define DR_LAUNCH(D)                                                                                                                  \
-    if ((size_t)2 * (DR_TC * (3 * D + 32) + DR_TC) * sizeof(float) > 48 * 1024) {                                                      \
+    {                                                                                                                                 \
         static bool attr_set = false;                                                                                                 \
         if (!attr_set && cudaFuncSetAttribute(delta_scan_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,                      \
-                                              (int)(2 * (DR_TC * (3 * D + 32) + DR_TC) * sizeof(float))) != cudaSuccess)            \
+                                              KESTREL_SMEM_MAX_DYNAMIC) != cudaSuccess)                                               \
             return kestrel_fail(-3, "delta_scan: cannot set the shared memory size");                                                 \
         attr_set = true;                                                                                                              \
     }                                                                                                                                 \
-    kestrel_launch(delta_scan_kernel<D>, grid, dim3(128), (size_t)2 * (DR_TC * (3 * D + 32) + DR_TC) * sizeof(float), stream, qn, kn, decay, act, C, col_v, \
-                   beta, state, (size_t)state_stride, cu_seqlens, slots, out, H, G, d, dv)
+    kestrel_launch(delta_scan_kernel<D>, grid, dim3(128),                                                                             \
+                   kestrel_spread_smem((long)grid.x * grid.y * grid.z, (size_t)2 * (DR_TC * (3 * D + 32) + DR_TC) * sizeof(float)),   \
+                   stream, qn, kn, decay, act, C, col_v, beta, state, (size_t)state_stride, cu_seqlens, slots, out, H, G, d, dv)
     if (d <= 32) { DR_LAUNCH(32); }
     else if (d <= 64) { DR_LAUNCH(64); }
     else if (d <= 128) { DR_LAUNCH(128); }

@@ -30,7 +30,18 @@
 #define TC_BK 64
 #define TC_THREADS 192
 
-enum { TC_PARTIAL = 0, TC_SWIGLU = 1, TC_PARTIAL2 = 2, TC_SWIGLU_T = 3, TC_QKV_PREP = 4 };     // PARTIAL2: two weight tiles a CTA, as SWIGLU, both written as float32 slices
+enum { TC_PARTIAL = 0, TC_SWIGLU = 1, TC_PARTIAL2 = 2, TC_SWIGLU_T = 3, TC_QKV_PREP = 4, TC_ACT = 5 };     // PARTIAL2: two weight tiles a CTA, as SWIGLU, both written as float32 slices
+// ACT (CTA pairs only): the PARTIAL product whose epilogue applies an activation to the accumulator
+// and writes the storage type, out bf16 [T, N] = act(x w^T) - a feed-forward's first product without
+// a gate: the float32 plane is neither written nor read back.  The kernel's `up_row_offset` argument
+// carries the activation: 1 the square of relu, 2 tanh, 3 silu (the numbering and the arithmetic of
+// the elementwise kernel that serves the product when it comes as slices: same bits).
+__device__ __forceinline__ float tc_act(float z, int act) {
+    if (act == 1) { const float r = fmaxf(z, 0.f); return r * r; }
+    if (act == 2) return tanhf(z);
+    if (act == 3) return z / (1.0f + expf(-z));
+    return z;
+}
 // QKV_PREP (CTA pairs only): the q, k, v product with the tokens as the M operand and, in its
 // epilogue, everything the prepare kernel does between that product and attention for head
 // size 128: bias, per-head RMSNorm, rotate-half rotation, queries out, keys and values into their
@@ -731,6 +742,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                                 o[(size_t)(t0 + c + jj) * ldo + n] = __float2bfloat16_rn(a * u[jj]);
                             }
                     }
+                } else if (MODE == TC_ACT) {
+                    __nv_bfloat16 *o = (__nv_bfloat16 *)out;
+                    if (n < N) {
+#pragma unroll
+                        for (int jj = 0; jj < 16; ++jj)
+                            if (c + jj < valid) o[(size_t)(t0 + c + jj) * ldo + n] = __float2bfloat16_rn(tc_act(g[jj], up_row_offset));
+                    }
                 } else if (n < N) {
                     float *o = (float *)out + (size_t)split * slice_stride;
                     if (accumulate) {           // out is the residual stream: the product is added to it in place
@@ -1113,6 +1131,24 @@ KESTREL_API int kestrel_gemm_tc_add(const void *x, const void *w, float *residua
     rc = kestrel_tensor_map_bf16(&mx, x, T, K, ldx, TCP_BN / 2);
     if (rc) return rc;
     return launch_tc_pair<TC_PARTIAL>(mw, mx, residual, T, N, K, ldo, 0, 1, 1, 0, stream);
+}
+
+// out bf16 [T, N] = act(x w^T) in the product's epilogue (ACT above; many tokens on CTA pairs only).
+// Returns 0 when done, 1 when this product cannot do it (few tokens, a product that is better cut
+// along K, pairs that cannot be scheduled) and nothing was launched: the caller then takes the
+// product as slices and lets an elementwise kernel apply the activation.
+KESTREL_API int kestrel_gemm_tc_act(const void *x, const void *w, void *out, int act, int T, int N, int K, long long ldx, long long ldw,
+                                    long long ldo, cudaStream_t stream) {
+    if (T == 0) return 0;
+    KESTREL_REQUIRE(act >= 1 && act <= 3, "gemm_tc_act: unknown activation %d", act);
+    if (T <= g_pair_min_tokens || !g_persistent || !g_pairs || !kestrel_gemm_tc_supported(x, w, T, N, K, ldx, ldw)) return 1;
+    if (kestrel_gemm_tc_splits(T, N, K) > 1) return 1;
+    CUtensorMap mw, mx;
+    int rc = kestrel_tensor_map_bf16(&mw, w, N, K, ldw, TC_BM);
+    if (rc) return rc;
+    rc = kestrel_tensor_map_bf16(&mx, x, T, K, ldx, TCP_BN / 2);
+    if (rc) return rc;
+    return launch_tc_pair<TC_ACT>(mw, mx, out, T, N, K, ldo, act, 0, 1, 0, stream);
 }
 
 // The q, k, v product of a prompt portion and everything between it and attention in one kernel

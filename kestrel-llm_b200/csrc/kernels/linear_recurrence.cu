@@ -266,13 +266,13 @@ template <int D, bool RANK1>
 static int lr_launch(dim3 grid, cudaStream_t stream, const float *r, const float *w, const float *k, const float *v, const float *a,
                      const float *b, float *state, size_t state_stride, size_t state_off, const int *cu_seqlens, const int *slots, float *out,
                      int H, int d, int dv) {
-    constexpr size_t smem = (size_t)2 * LR_TC * ((RANK1 ? 5 : 3) * D + 32) * sizeof(float);
-    if (smem > 48 * 1024) {
-        static bool attr_set = false;
-        if (!attr_set && cudaFuncSetAttribute(recurrence_scan_kernel<D, RANK1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return kestrel_fail(-3, "recurrence_scan: cannot set the shared memory size");
-        attr_set = true;
-    }
+    constexpr size_t smem_need = (size_t)2 * LR_TC * ((RANK1 ? 5 : 3) * D + 32) * sizeof(float);
+    static bool attr_set = false;
+    if (!attr_set && cudaFuncSetAttribute(recurrence_scan_kernel<D, RANK1>, cudaFuncAttributeMaxDynamicSharedMemorySize, KESTREL_SMEM_MAX_DYNAMIC) != cudaSuccess)
+        return kestrel_fail(-3, "recurrence_scan: cannot set the shared memory size");
+    attr_set = true;
+    // a prompt's scan is few CTAs that run for hundreds of microseconds: one SM each (kestrel_spread_smem)
+    const size_t smem = kestrel_spread_smem((long)grid.x * grid.y * grid.z, smem_need);
     kestrel_launch(recurrence_scan_kernel<D, RANK1>, grid, dim3(128), smem, stream, r, w, k, v, a, b, state, state_stride, state_off, cu_seqlens,
                    slots, out, H, d, dv);
     return kestrel_check_launch("recurrence_scan");

@@ -252,6 +252,12 @@ KESTREL_API int kestrel_combine_normed(const float *a, int Sa, long long stride_
                                        const float *wb, float eps, float mix, float *out, int T, int d, cudaStream_t stream) {
     if (T == 0) return 0;
     KESTREL_REQUIRE(T > 0 && d > 0 && Sa > 0 && Sb > 0 && d <= 12000, "combine_normed: bad sizes T=%d d=%d", T, d);
+    if ((size_t)2 * d * sizeof(float) > 48 * 1024) {          // both rows of a wide model: more shared memory than a kernel gets unasked
+        static bool attr_set = false;
+        if (!attr_set && cudaFuncSetAttribute(combine_normed_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 12000 * 2 * (int)sizeof(float)) != cudaSuccess)
+            return kestrel_fail(-3, "combine_normed: cannot set the shared memory size");
+        attr_set = true;
+    }
     kestrel_launch(combine_normed_kernel, dim3(T), dim3(GN_THREADS), (size_t)2 * d * sizeof(float), stream, a, Sa, (size_t)stride_a, wa, b, Sb,
                    (size_t)stride_b, wb, eps, mix, out, d);
     return kestrel_check_launch("combine_normed");
@@ -341,20 +347,22 @@ KESTREL_API int kestrel_embed_add(const void *table, int dtype, const int *ids, 
 // ------------------------------------------------------------------------------------------
 // logits <- logits * scale, then cap * tanh(logits / cap) where cap > 0; in place, float32
 // ------------------------------------------------------------------------------------------
-__global__ void logit_scale_cap_kernel(float *__restrict__ logits, size_t ld, int V, float scale, float cap) {
+__global__ void logit_scale_cap_kernel(float *__restrict__ logits, size_t ld, int R, int V, float scale, float cap) {
     pdl_launch_dependents();
     pdl_wait();
-    float *row = logits + (size_t)blockIdx.y * ld;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= V) return;
-    float z = row[i] * scale;
-    if (cap > 0.f) z = cap * tanhf(z / cap);
-    row[i] = z;
+    for (int r = blockIdx.y; r < R; r += gridDim.y) {
+        float *row = logits + (size_t)r * ld;
+        float z = row[i] * scale;
+        if (cap > 0.f) z = cap * tanhf(z / cap);
+        row[i] = z;
+    }
 }
 
 KESTREL_API int kestrel_logit_scale_cap(float *logits, long long ld, int R, int V, float scale, float cap, cudaStream_t stream) {
     if (R == 0) return 0;
-    KESTREL_REQUIRE(R > 0 && R <= 65535 && V > 0 && cap >= 0.f, "logit_scale_cap: bad sizes R=%d V=%d", R, V);
-    kestrel_launch(logit_scale_cap_kernel, dim3((V + 255) / 256, R), dim3(256), 0, stream, logits, (size_t)ld, V, scale, cap);
+    KESTREL_REQUIRE(R > 0 && V > 0 && cap >= 0.f, "logit_scale_cap: bad sizes R=%d V=%d", R, V);
+    kestrel_launch(logit_scale_cap_kernel, dim3((V + 255) / 256, R < 32768 ? R : 32768), dim3(256), 0, stream, logits, (size_t)ld, R, V, scale, cap);
     return kestrel_check_launch("logit_scale_cap");
 }

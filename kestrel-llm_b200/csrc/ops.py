@@ -492,6 +492,24 @@ def linear_add_into(x: torch.Tensor, w: torch.Tensor, residual: torch.Tensor) ->
     return True
 
 
+def linear_act(x: torch.Tensor, w: torch.Tensor, act: str, weights_static: bool = False) -> torch.Tensor:
+    """act(x w^T) in x's dtype, ``act`` one of `COLUMN_ACTS`.  bfloat16 with many tokens: the activation is the
+    product's epilogue and the float32 product never reaches memory; otherwise the product comes as slices and
+    `partial_columns_act` sums and activates them.  Both ways give the same bits where the product is one slice."""
+    T, N = x.shape[0], w.shape[0]
+    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.dim() == 2 and linear_act_fused:
+        out = torch.empty((T, N), dtype=torch.bfloat16, device=x.device)
+        rc = library().kestrel_gemm_tc_act(x.data_ptr(), w.data_ptr(), out.data_ptr(), COLUMN_ACTS[act], T, N, x.shape[1], x.stride(0),
+                                           w.stride(0), out.stride(0), _stream())
+        if rc != 1:
+            _check(rc)
+            return out
+    return partial_columns_act(Partials(linear(x, w, weights_static=weights_static)), 0, N, x.dtype, act)
+
+
+linear_act_fused = True          # tests switch the epilogue form off to hold both forms against each other
+
+
 def gate_up_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, ff: int, weights_static: bool = False) -> torch.Tensor:
     """silu(x Wg^T) * (x Wu^T) in x's dtype, Wg and Wu being the two halves of w_gate_up's rows.
     ``weights_static`` as in `gemm_tc`."""

@@ -249,6 +249,7 @@ KESTREL_API int kestrel_gemm_tc_plan(const void *x, const void *w, int T, int N,
 KESTREL_API int kestrel_gemm_tc_w(const void *x, const void *w, float *out, int T, int N, int K, long long ldx, long long ldw, long long ldo, int splits, long long slice_stride, int weights_static, kestrel_stream_t stream);
 KESTREL_API int kestrel_gemm_tc(const void *x, const void *w, float *out, int T, int N, int K, long long ldx, long long ldw, long long ldo, int splits, long long slice_stride, kestrel_stream_t stream);
 KESTREL_API int kestrel_gemm_tc_add(const void *x, const void *w, float *residual, int T, int N, int K, long long ldx, long long ldw, long long ldo, kestrel_stream_t stream);
+KESTREL_API int kestrel_gemm_tc_act(const void *x, const void *w, void *out, int act, int T, int N, int K, long long ldx, long long ldw, long long ldo, kestrel_stream_t stream);
 KESTREL_API int kestrel_gemm_tc_swiglu_w(const void *x, const void *w, void *out, int T, int ff, int K, long long ldx, long long ldw, long long ldo, int weights_static, kestrel_stream_t stream);
 KESTREL_API int kestrel_gemm_tc_swiglu(const void *x, const void *w, void *out, int T, int ff, int K, long long ldx, long long ldw, long long ldo, kestrel_stream_t stream);
 /* the q, k, v product of many tokens with the prepare kernel's work in its epilogue (head size 128, rotate-half over the whole head); 0 done, 1 this form does not apply and nothing ran */

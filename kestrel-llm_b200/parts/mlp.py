@@ -58,5 +58,5 @@ class DenseMLP(FeedForward):
         return [WeightSlot(self.prefix + self.names[0], self.up.weight), WeightSlot(self.prefix + self.names[1], self.down.weight)]
 
     def forward(self, x: torch.Tensor, batch) -> ops.Partials:
-        act = ops.partial_columns_act(self.up.forward(x), 0, self.intermediate, self.dtype, self.activation)
-        return self.down.forward(act)
+        # many tokens in bfloat16: the activation is the up product's epilogue; otherwise its slices are summed and activated
+        return self.down.forward(ops.linear_act(x, self.up.weight, self.activation, weights_static=True))

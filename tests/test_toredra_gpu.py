@@ -295,6 +295,35 @@ def test_block_gates_norms_and_feed_forward():
         assert np.abs(P.layer_forward(x.copy(), gated_off, cfg, 0) - want).max() > 0.05 * np.abs(want).max()
 
 
+@pytest.mark.parametrize("act", ["relu2", "tanh", "silu"])
+@pytest.mark.parametrize("T_,N,K", [(129, 264, 72), (700, 1024, 256), (2048, 520, 136), (64, 256, 64), (300, 100, 70)])
+def test_activation_in_the_products_epilogue(act, T_, N, K):
+    """bfloat16: act(x w^T) with the activation as the epilogue of the tcgen05 product on CTA pairs (many tokens, sizes
+    the product takes uncut) against the product's slices summed and activated by the elementwise kernel - the same
+    bits - and against numpy; few tokens and sizes that are no multiples of 8 take the second way by themselves."""
+    import torch
+    from kestrel_llm_b200.csrc import ops
+    rng = np.random.default_rng(T_ + N)
+    x = torch.from_numpy(rng.standard_normal((T_, K)).astype(np.float32)).to(torch.bfloat16)
+    w = torch.from_numpy((rng.standard_normal((N, K)) / np.sqrt(K)).astype(np.float32)).to(torch.bfloat16)
+    xd, wd = x.to("cuda:0"), w.to("cuda:0")
+    fused = ops.linear_act(xd, wd, act)
+    ops.raise_on_kernel_error()
+    ops.linear_act_fused = False
+    try:
+        slices = ops.linear_act(xd, wd, act)
+    finally:
+        ops.linear_act_fused = True
+    z = x.to(torch.float64).numpy() @ w.to(torch.float64).numpy().T
+    want = {"relu2": np.maximum(z, 0.0) ** 2, "tanh": np.tanh(z), "silu": z / (1.0 + np.exp(-z))}[act]
+    assert fused.dtype == torch.bfloat16 and tuple(fused.shape) == (T_, N)
+    _close(fused.float().cpu().numpy(), want, "bfloat16", f"{act} in the epilogue", scale=max(1.0, float(np.abs(want).max())))
+    if ops.library().kestrel_gemm_tc_plan(xd.data_ptr(), wd.data_ptr(), T_, N, K, xd.stride(0), wd.stride(0)) == 1:
+        assert torch.equal(fused, slices)
+    else:
+        _close(slices.float().cpu().numpy(), want, "bfloat16", f"{act} on slices", scale=max(1.0, float(np.abs(want).max())))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("scale,cap", [(1.0, 0.0), (2.5, 0.0), (1.0, 7.0), (0.3, 4.0)])
 def test_output_head_scales_then_caps(dtype, scale, cap):
