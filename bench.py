@@ -411,9 +411,14 @@ def run_zidivik(args) -> int:
         dec = timed(decode, K) / K
         launches = (ops.launches + engine.graph_launches + engine.native_launches - before) // K
         if not clocks.rows:                      # the timed regions were shorter than the sampler's period: the same steps
-            until = time.time() + 0.7            # once more, untimed, so that the record has clocks under this load
+            until = time.time() + 0.7            # once more, untimed, so that the record has clocks under this load; decode
+            extra = 0                            # steps while the requests' page head-room lasts, prompt steps after that
             while time.time() < until:
-                decode()
+                if extra < 64:
+                    decode()
+                else:
+                    prefill()
+                extra += 1
             torch.cuda.synchronize()
 
         # device time per kind of operation, one step of each

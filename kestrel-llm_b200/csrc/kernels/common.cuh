@@ -93,16 +93,33 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
-// Sum of a product's float32 slices at one element, in ascending slice order; the loads of four
-// slices are in flight at once (the adds keep their order, so the bits are those of a plain loop).
+// Sum of a product's float32 slices at one element, in ascending slice order; the loads of eight
+// (then four) slices are in flight at once (the adds keep their order, so the bits are those of a
+// plain loop).
 __device__ __forceinline__ float sum_slices(const float *__restrict__ p, int S, size_t slice_stride, size_t off) {
     float v = 0.f;
     int s = 0;
+    for (; s + 8 <= S; s += 8) {
+        float x[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] = p[(size_t)(s + j) * slice_stride + off];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v += x[j];
+    }
     for (; s + 4 <= S; s += 4) {
         const float a = p[(size_t)s * slice_stride + off], b = p[(size_t)(s + 1) * slice_stride + off];
         const float c = p[(size_t)(s + 2) * slice_stride + off], d = p[(size_t)(s + 3) * slice_stride + off];
         v += a; v += b; v += c; v += d;
     }
-    for (; s < S; ++s) v += p[(size_t)s * slice_stride + off];
+    const int rest = S - s;                           // up to three more: their loads in flight together as well
+    if (rest == 3) {
+        const float a = p[(size_t)s * slice_stride + off], b = p[(size_t)(s + 1) * slice_stride + off], c = p[(size_t)(s + 2) * slice_stride + off];
+        v += a; v += b; v += c;
+    } else if (rest == 2) {
+        const float a = p[(size_t)s * slice_stride + off], b = p[(size_t)(s + 1) * slice_stride + off];
+        v += a; v += b;
+    } else if (rest == 1) {
+        v += p[(size_t)s * slice_stride + off];
+    }
     return v;
 }

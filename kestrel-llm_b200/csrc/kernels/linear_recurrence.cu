@@ -30,7 +30,7 @@ __device__ __forceinline__ float lr_sigmoid(float z) { return 1.0f / (1.0f + exp
 
 // ---- gates of the forget-gate recurrence -------------------------------------------------------
 // product columns: q at col_q, f at col_f (n = H d each), v at col_v (nv = H dv)
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 forget_gates_kernel(const float *__restrict__ p, int S, size_t slice_stride, int ld, int col_q, int col_f, int col_v,
                     const float *__restrict__ f_bias, const float *__restrict__ lower, float *__restrict__ r_out,
                     float *__restrict__ w_out, float *__restrict__ k_out, float *__restrict__ v_out, int n, int nv) {
@@ -52,9 +52,70 @@ forget_gates_kernel(const float *__restrict__ p, int S, size_t slice_stride, int
 
 // ---- gates of the generalised delta rule -------------------------------------------------------
 // product columns: r, k, v, rate logits at col_r, col_k, col_v, col_a (H d each); the decay's logits are a second
-// product `wz` [T, H d]; a warp a head
+// product `wz` [T, H d]; a warp a head, J = ceil(d / 32) channels a lane
+template <int J>
 __global__ void __launch_bounds__(128)
 removal_gates_kernel(const float *__restrict__ p, int S, size_t slice_stride, int ld, int col_r, int col_k, int col_v, int col_a,
+                     const float *__restrict__ a_bias, const float *__restrict__ wz, int Sw, size_t w_stride,
+                     const float *__restrict__ w_bias, float decay_rate, float *__restrict__ r_out, float *__restrict__ k_out,
+                     float *__restrict__ v_out, float *__restrict__ w_out, float *__restrict__ a_out, float *__restrict__ b_out,
+                     int H, int d) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t row = (size_t)t * ld, n = (size_t)H * d;
+    for (int h = blockIdx.y * 4 + warp; h < H; h += gridDim.y * 4) {
+        // Slice by slice, all of a lane's loads of a slice in flight at once: a step of few tokens is bound by their
+        // latency.  Every element's sum runs over the slices in ascending order from 0, as sum_slices does: same bits.
+        float k[J], ar[J], z[J], r[J], v[J];
+        int cc[J];
+#pragma unroll
+        for (int j = 0; j < J; ++j) {
+            const int i = lane + 32 * j;
+            cc[j] = h * d + (i < d ? i : d - 1);              // lanes past the head's end load its last channel and drop it
+            k[j] = ar[j] = z[j] = r[j] = v[j] = 0.f;
+        }
+        for (int s = 0; s < S; ++s) {
+            const float *ps = p + (size_t)s * slice_stride + row;
+#pragma unroll
+            for (int j = 0; j < J; ++j) {
+                k[j] += ps[col_k + cc[j]];
+                ar[j] += ps[col_a + cc[j]];
+                r[j] += ps[col_r + cc[j]];
+                v[j] += ps[col_v + cc[j]];
+            }
+        }
+        for (int s = 0; s < Sw; ++s) {
+            const float *ps = wz + (size_t)s * w_stride + (size_t)t * n;
+#pragma unroll
+            for (int j = 0; j < J; ++j) z[j] += ps[cc[j]];
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < J; ++j)
+            if (lane + 32 * j < d) ss = fmaf(k[j], k[j], ss);
+        ss = warp_sum(ss);
+        const float inv = 1.0f / sqrtf(ss + 1e-6f);
+#pragma unroll
+        for (int j = 0; j < J; ++j) {
+            const int i = lane + 32 * j, c = h * d + i;
+            if (i >= d) continue;
+            const size_t o = (size_t)t * n + c;
+            const float u = k[j] * inv;
+            const float rate = lr_sigmoid(ar[j] + (a_bias ? a_bias[c] : 0.f));
+            r_out[o] = r[j];
+            k_out[o] = k[j];
+            v_out[o] = v[j];
+            w_out[o] = expf(-decay_rate * lr_sigmoid(z[j] + (w_bias ? w_bias[c] : 0.f)));
+            a_out[o] = -(rate * u);
+            b_out[o] = u;
+        }
+    }
+}
+
+// the same gates for a step of many tokens: blocks enough to hide the loads, an element at a time (same sums, same bits)
+__global__ void __launch_bounds__(128)
+removal_gates_stream_kernel(const float *__restrict__ p, int S, size_t slice_stride, int ld, int col_r, int col_k, int col_v, int col_a,
                      const float *__restrict__ a_bias, const float *__restrict__ wz, int Sw, size_t w_stride,
                      const float *__restrict__ w_bias, float decay_rate, float *__restrict__ r_out, float *__restrict__ k_out,
                      float *__restrict__ v_out, float *__restrict__ w_out, float *__restrict__ a_out, float *__restrict__ b_out,
@@ -159,9 +220,7 @@ recurrence_scan_kernel(const float *__restrict__ r, const float *__restrict__ w,
         const float *sk = sm + (size_t)stage * STAGE, *sr = sk + LR_TC * D, *sw = sr + LR_TC * D;
         const float *sa = sw + LR_TC * D, *sb = sa + (RANK1 ? LR_TC * D : 0), *sv = sb + (RANK1 ? LR_TC * D : 0);
         const int n = min(LR_TC, t1 - tb);
-#pragma unroll
-        for (int c = 0; c < LR_TC; ++c) {             // unrolled: the next token's operands are fetched under this token's chain
-            if (c >= n) break;
+        auto token = [&](int c) -> float {
             const float4 *k4 = reinterpret_cast<const float4 *>(sk + c * D), *r4 = reinterpret_cast<const float4 *>(sr + c * D),
                          *w4 = reinterpret_cast<const float4 *>(sw + c * D), *a4 = reinterpret_cast<const float4 *>(sa + c * D),
                          *b4 = reinterpret_cast<const float4 *>(sb + c * D);
@@ -195,10 +254,35 @@ recurrence_scan_kernel(const float *__restrict__ r, const float *__restrict__ w,
                 Sc[m][2] = fmaf(ww.z, Sc[m][2], e2); s2 = fmaf(Sc[m][2], rr.z, s2);
                 Sc[m][3] = fmaf(ww.w, Sc[m][3], e3); s3 = fmaf(Sc[m][3], rr.w, s3);
             }
-            float o = (s0 + s1) + (s2 + s3);
+            return (s0 + s1) + (s2 + s3);             // this thread's part of the read-out; the lanes' parts are summed below
+        };
+        auto reduce_store = [&](int c, float o) {
 #pragma unroll
             for (int sh = 1; sh < LR_LPC; sh <<= 1) o += __shfl_xor_sync(0xffffffffu, o, sh);
             if (live && part == 0) out[((size_t)(tb + c) * H + h) * dv + j] = o;
+        };
+        // A full stage is one block of code, so that the next token's operands are fetched under this token's chain.
+        if (n == LR_TC && (!RANK1 || D <= 32)) {
+            // The read-outs of the stage's tokens go through the shuffle tree together at its end, eight independent chains
+            // instead of one after every token (290 instead of 436 us for 2,048 tokens of 16 heads without the correction;
+            // with it and 128 channels the eight held sums cost more registers than the chains cost time, so it reads out
+            // token by token).  The tree is the same one either way: same bits.
+            float o[LR_TC];
+#pragma unroll
+            for (int c = 0; c < LR_TC; ++c) o[c] = token(c);
+#pragma unroll
+            for (int sh = 1; sh < LR_LPC; sh <<= 1)
+#pragma unroll
+                for (int c = 0; c < LR_TC; ++c) o[c] += __shfl_xor_sync(0xffffffffu, o[c], sh);
+            if (live && part == 0) {
+#pragma unroll
+                for (int c = 0; c < LR_TC; ++c) out[((size_t)(tb + c) * H + h) * dv + j] = o[c];
+            }
+        } else if (n == LR_TC) {
+#pragma unroll
+            for (int c = 0; c < LR_TC; ++c) reduce_store(c, token(c));
+        } else {
+            for (int c = 0; c < n; ++c) reduce_store(c, token(c));
         }
         __syncthreads();                              // the stage may be filled again
     }
@@ -243,7 +327,8 @@ KESTREL_API int kestrel_forget_gates(const float *partial, int S, long long slic
     if (T == 0) return 0;
     KESTREL_REQUIRE(T > 0 && S > 0 && n > 0 && nv > 0 && col_q >= 0 && col_f >= 0 && col_v >= 0 && col_q + n <= ld && col_f + n <= ld && col_v + nv <= ld,
                     "forget_gates: bad sizes");
-    kestrel_launch(forget_gates_kernel, dim3(T), dim3(256), 0, stream, partial, S, (size_t)slice_stride, ld, col_q, col_f, col_v, f_bias, lower,
+    // elementwise: any block size gives the same bits; a step of few tokens has few blocks, so each gets more threads
+    kestrel_launch(forget_gates_kernel, dim3(T), dim3(T >= 512 ? 256 : 1024), 0, stream, partial, S, (size_t)slice_stride, ld, col_q, col_f, col_v, f_bias, lower,
                    r_out, w_out, k_out, v_out, n, nv);
     return kestrel_check_launch("forget_gates");
 }
@@ -255,10 +340,19 @@ KESTREL_API int kestrel_removal_gates(const float *partial, int S, long long sli
     if (T == 0) return 0;
     const int n = H * d;
     KESTREL_REQUIRE(T > 0 && S > 0 && Sw > 0 && H > 0 && d > 0 && col_r >= 0 && col_k >= 0 && col_v >= 0 && col_a >= 0 && col_r + n <= ld &&
-                    col_k + n <= ld && col_v + n <= ld && col_a + n <= ld, "removal_gates: bad sizes");
+                    col_k + n <= ld && col_v + n <= ld && col_a + n <= ld && d <= 256, "removal_gates: bad sizes");
     const int by = T >= 512 ? 1 : (H + 3) / 4;
-    kestrel_launch(removal_gates_kernel, dim3(T, by), dim3(128), 0, stream, partial, S, (size_t)slice_stride, ld, col_r, col_k, col_v, col_a, a_bias,
+    if (T >= 512) {
+        kestrel_launch(removal_gates_stream_kernel, dim3(T, by), dim3(128), 0, stream, partial, S, (size_t)slice_stride, ld, col_r, col_k, col_v, col_a, a_bias,
                    wz, Sw, (size_t)w_stride, w_bias, decay_rate, r_out, k_out, v_out, w_out, a_out, b_out, H, d);
+        return kestrel_check_launch("removal_gates");
+    }
+#define RG_LAUNCH(J) kestrel_launch(removal_gates_kernel<J>, dim3(T, by), dim3(128), 0, stream, partial, S, (size_t)slice_stride, ld, col_r, col_k, col_v, col_a, a_bias, \
+                   wz, Sw, (size_t)w_stride, w_bias, decay_rate, r_out, k_out, v_out, w_out, a_out, b_out, H, d)
+    if (d <= 64) RG_LAUNCH(2);
+    else if (d <= 128) RG_LAUNCH(4);
+    else RG_LAUNCH(8);
+#undef RG_LAUNCH
     return kestrel_check_launch("removal_gates");
 }
 

@@ -210,15 +210,28 @@ KESTREL_API int kestrel_partial_columns_act(const float *p, int S, long long sli
 // ------------------------------------------------------------------------------------------
 // Block-wide sum in a fixed tree: lanes by shuffle, warps in ascending order.  Every thread gets it.
 // ------------------------------------------------------------------------------------------
-#define GN_THREADS 256
-__device__ __forceinline__ float gn_block_sum(float v, float *red) {
-    v = warp_sum(v);
+// A block takes one row of width d and sums over it as VT = gn_threads(d) "virtual threads" would: virtual
+// thread u owns the elements u, u + VT, u + 2 VT, ... in ascending order, 32 consecutive ones add in a
+// shuffle tree, and the VT / 32 sums are added in ascending order.  VT depends on d alone, so every bit
+// of a row is the same whether the step has one token or thousands.  How many REAL threads play them is
+// free: a step of few tokens has few blocks, each bound by the latency of its loads, and gets VT threads
+// (Q = 1: all of a row's loads in flight at once); a step of many tokens gets VT / Q threads that each
+// keep Q partial sums, which loads the SMs more evenly.
+#define GN_VT_MAX 1024
+static inline int gn_threads(int d) { return d >= 1024 ? 1024 : d >= 512 ? 512 : 256; }
+static inline int gn_fold(int T, int d) { return T >= 256 ? gn_threads(d) / 256 : 1; }        // Q: 1, 2 or 4
+template <int Q>
+__device__ __forceinline__ float gn_block_sum(const float (&part)[Q], float *red) {
+    const int warps = blockDim.x >> 5;
     __syncthreads();                                  // red may still be read from the sum before
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+#pragma unroll
+    for (int q = 0; q < Q; ++q) {
+        const float v = warp_sum(part[q]);
+        if ((threadIdx.x & 31) == 0) red[q * warps + (threadIdx.x >> 5)] = v;
+    }
     __syncthreads();
     float tot = 0.f;
-#pragma unroll
-    for (int k = 0; k < GN_THREADS / 32; ++k) tot += red[k];
+    for (int k = 0; k < Q * warps; ++k) tot += red[k];
     return tot;
 }
 
@@ -226,26 +239,34 @@ __device__ __forceinline__ float gn_block_sum(float v, float *red) {
 // Two products side by side, each normalised over the row with a weight of its own, then mixed:
 // out[t] = mix * (a / sqrt(mean(a^2) + eps) * wa + b / sqrt(mean(b^2) + eps) * wb), float32.
 // ------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(GN_THREADS)
+template <int Q>
+__global__ void __launch_bounds__(GN_VT_MAX / Q)
 combine_normed_kernel(const float *__restrict__ a, int Sa, size_t stride_a, const float *__restrict__ wa, const float *__restrict__ b, int Sb,
                       size_t stride_b, const float *__restrict__ wb, float eps, float mix, float *__restrict__ out, int d) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float cn_rows[];               // a's row, then b's
-    __shared__ float red[GN_THREADS / 32];
-    const int t = blockIdx.x;
+    __shared__ float red[GN_VT_MAX / 32];
+    const int t = blockIdx.x, nt = blockDim.x;
     float *ra = cn_rows, *rb = cn_rows + d;
-    float sa = 0.f, sb = 0.f;
-    for (int i = threadIdx.x; i < d; i += GN_THREADS) {
-        const float x = sum_slices(a, Sa, stride_a, (size_t)t * d + i), y = sum_slices(b, Sb, stride_b, (size_t)t * d + i);
-        ra[i] = x;
-        rb[i] = y;
-        sa = fmaf(x, x, sa);
-        sb = fmaf(y, y, sb);
+    float sa[Q], sb[Q];
+#pragma unroll
+    for (int q = 0; q < Q; ++q) sa[q] = sb[q] = 0.f;
+#pragma unroll
+    for (int q = 0; q < Q; ++q) {                    // one partial sum live at a time: few registers, many warps an SM
+        for (int i = q * nt + threadIdx.x; i < d; i += Q * nt) {
+            {
+                const float x = sum_slices(a, Sa, stride_a, (size_t)t * d + i), y = sum_slices(b, Sb, stride_b, (size_t)t * d + i);
+                ra[i] = x;
+                rb[i] = y;
+                sa[q] = fmaf(x, x, sa[q]);
+                sb[q] = fmaf(y, y, sb[q]);
+            }
+        }
     }
-    const float na = 1.0f / sqrtf(gn_block_sum(sa, red) / (float)d + eps);
-    const float nb = 1.0f / sqrtf(gn_block_sum(sb, red) / (float)d + eps);
-    for (int i = threadIdx.x; i < d; i += GN_THREADS) out[(size_t)t * d + i] = mix * (ra[i] * na * wa[i] + rb[i] * nb * wb[i]);
+    const float na = 1.0f / sqrtf(gn_block_sum<Q>(sa, red) / (float)d + eps);
+    const float nb = 1.0f / sqrtf(gn_block_sum<Q>(sb, red) / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += nt) out[(size_t)t * d + i] = mix * (ra[i] * na * wa[i] + rb[i] * nb * wb[i]);
 }
 
 KESTREL_API int kestrel_combine_normed(const float *a, int Sa, long long stride_a, const float *wa, const float *b, int Sb, long long stride_b,
@@ -254,12 +275,19 @@ KESTREL_API int kestrel_combine_normed(const float *a, int Sa, long long stride_
     KESTREL_REQUIRE(T > 0 && d > 0 && Sa > 0 && Sb > 0 && d <= 12000, "combine_normed: bad sizes T=%d d=%d", T, d);
     if ((size_t)2 * d * sizeof(float) > 48 * 1024) {          // both rows of a wide model: more shared memory than a kernel gets unasked
         static bool attr_set = false;
-        if (!attr_set && cudaFuncSetAttribute(combine_normed_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 12000 * 2 * (int)sizeof(float)) != cudaSuccess)
+        if (!attr_set && (cudaFuncSetAttribute(combine_normed_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 12000 * 2 * (int)sizeof(float)) != cudaSuccess ||
+                          cudaFuncSetAttribute(combine_normed_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 12000 * 2 * (int)sizeof(float)) != cudaSuccess ||
+                          cudaFuncSetAttribute(combine_normed_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 12000 * 2 * (int)sizeof(float)) != cudaSuccess))
             return kestrel_fail(-3, "combine_normed: cannot set the shared memory size");
         attr_set = true;
     }
-    kestrel_launch(combine_normed_kernel, dim3(T), dim3(GN_THREADS), (size_t)2 * d * sizeof(float), stream, a, Sa, (size_t)stride_a, wa, b, Sb,
-                   (size_t)stride_b, wb, eps, mix, out, d);
+    const int Q = gn_fold(T, d);
+#define CN_LAUNCH(QQ) kestrel_launch(combine_normed_kernel<QQ>, dim3(T), dim3(gn_threads(d) / QQ), (size_t)2 * d * sizeof(float), stream, a, Sa, (size_t)stride_a, wa, b, Sb, \
+                   (size_t)stride_b, wb, eps, mix, out, d)
+    if (Q == 4) CN_LAUNCH(4);
+    else if (Q == 2) CN_LAUNCH(2);
+    else CN_LAUNCH(1);
+#undef CN_LAUNCH
     return kestrel_check_launch("combine_normed");
 }
 
@@ -270,39 +298,50 @@ KESTREL_API int kestrel_combine_normed(const float *a, int Sa, long long stride_
 // and, where `next_w` is given, the next norm of the stream is made in the same pass:
 //     next_out[t] = residual[t] / sqrt(mean(residual[t]^2) + eps_next) * next_w       (storage type)
 // ------------------------------------------------------------------------------------------
-template <typename TOut>
-__global__ void __launch_bounds__(GN_THREADS)
+template <typename TOut, int Q>
+__global__ void __launch_bounds__(GN_VT_MAX / Q)
 add_gated_normed_kernel(float *__restrict__ residual, const float *__restrict__ y, int Sy, size_t stride_y, const float *__restrict__ y_bias,
                         const float *__restrict__ g, int Sg, size_t stride_g, const float *__restrict__ g_bias, const float *__restrict__ w,
                         float eps, const float *__restrict__ next_w, float eps_next, TOut *__restrict__ next_out, int d) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float gn_row[];
-    __shared__ float red[GN_THREADS / 32];
-    const int t = blockIdx.x;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < d; i += GN_THREADS) {
-        float v = sum_slices(y, Sy, stride_y, (size_t)t * d + i);
-        if (y_bias) v += y_bias[i];
-        if (g) {
-            float z = sum_slices(g, Sg, stride_g, (size_t)t * d + i);
-            if (g_bias) z += g_bias[i];
-            v *= 1.0f / (1.0f + expf(-z));
+    __shared__ float red[GN_VT_MAX / 32];
+    const int t = blockIdx.x, nt = blockDim.x;
+    float ss[Q], s2[Q];
+#pragma unroll
+    for (int q = 0; q < Q; ++q) ss[q] = s2[q] = 0.f;
+#pragma unroll
+    for (int q = 0; q < Q; ++q) {                    // one partial sum live at a time: few registers, many warps an SM
+        for (int i = q * nt + threadIdx.x; i < d; i += Q * nt) {
+            {
+                float v = sum_slices(y, Sy, stride_y, (size_t)t * d + i);
+                if (y_bias) v += y_bias[i];
+                if (g) {
+                    float z = sum_slices(g, Sg, stride_g, (size_t)t * d + i);
+                    if (g_bias) z += g_bias[i];
+                    v *= 1.0f / (1.0f + expf(-z));
+                }
+                gn_row[i] = v;
+                ss[q] = fmaf(v, v, ss[q]);
+            }
         }
-        gn_row[i] = v;
-        ss = fmaf(v, v, ss);
     }
-    const float rn = 1.0f / sqrtf(gn_block_sum(ss, red) / (float)d + eps);
-    float s2 = 0.f;
-    for (int i = threadIdx.x; i < d; i += GN_THREADS) {
-        const float x = residual[(size_t)t * d + i] + gn_row[i] * rn * w[i];
-        residual[(size_t)t * d + i] = x;
-        gn_row[i] = x;
-        s2 = fmaf(x, x, s2);
+    const float rn = 1.0f / sqrtf(gn_block_sum<Q>(ss, red) / (float)d + eps);
+#pragma unroll
+    for (int q = 0; q < Q; ++q) {                    // one partial sum live at a time: few registers, many warps an SM
+        for (int i = q * nt + threadIdx.x; i < d; i += Q * nt) {
+            {
+                const float x = residual[(size_t)t * d + i] + gn_row[i] * rn * w[i];
+                residual[(size_t)t * d + i] = x;
+                gn_row[i] = x;
+                s2[q] = fmaf(x, x, s2[q]);
+            }
+        }
     }
     if (!next_w) return;
-    const float r2 = 1.0f / sqrtf(gn_block_sum(s2, red) / (float)d + eps_next);
-    for (int i = threadIdx.x; i < d; i += GN_THREADS) next_out[(size_t)t * d + i] = from_f32<TOut>(gn_row[i] * r2 * next_w[i]);
+    const float r2 = 1.0f / sqrtf(gn_block_sum<Q>(s2, red) / (float)d + eps_next);
+    for (int i = threadIdx.x; i < d; i += nt) next_out[(size_t)t * d + i] = from_f32<TOut>(gn_row[i] * r2 * next_w[i]);
 }
 
 KESTREL_API int kestrel_add_gated_normed(float *residual, const float *y, int Sy, long long stride_y, const float *y_bias, const float *g, int Sg,
@@ -311,14 +350,15 @@ KESTREL_API int kestrel_add_gated_normed(float *residual, const float *y, int Sy
     if (T == 0) return 0;
     KESTREL_REQUIRE(T > 0 && d > 0 && Sy > 0 && (!g || Sg > 0) && d <= 12000 && ((next_w == nullptr) == (next_out == nullptr)),
                     "add_gated_normed: bad arguments T=%d d=%d", T, d);
-    if (next_dtype == KESTREL_F32 || !next_w)
-        kestrel_launch(add_gated_normed_kernel<float>, dim3(T), dim3(GN_THREADS), (size_t)d * sizeof(float), stream, residual, y, Sy, (size_t)stride_y, y_bias,
-                       g, Sg, (size_t)stride_g, g_bias, w, eps, next_w, eps_next, (float *)next_out, d);
-    else if (next_dtype == KESTREL_BF16)
-        kestrel_launch(add_gated_normed_kernel<__nv_bfloat16>, dim3(T), dim3(GN_THREADS), (size_t)d * sizeof(float), stream, residual, y, Sy, (size_t)stride_y,
-                       y_bias, g, Sg, (size_t)stride_g, g_bias, w, eps, next_w, eps_next, (__nv_bfloat16 *)next_out, d);
-    else
-        return kestrel_fail(-2, "add_gated_normed: unknown dtype %d", next_dtype);
+    const int Q = gn_fold(T, d);
+#define GN_LAUNCH(TT, QQ) kestrel_launch(add_gated_normed_kernel<TT, QQ>, dim3(T), dim3(gn_threads(d) / QQ), (size_t)d * sizeof(float), stream, residual, y, Sy, \
+                   (size_t)stride_y, y_bias, g, Sg, (size_t)stride_g, g_bias, w, eps, next_w, eps_next, (TT *)next_out, d)
+#define GN_LAUNCH_Q(TT) do { if (Q == 4) GN_LAUNCH(TT, 4); else if (Q == 2) GN_LAUNCH(TT, 2); else GN_LAUNCH(TT, 1); } while (0)
+    if (next_dtype == KESTREL_F32 || !next_w) GN_LAUNCH_Q(float);
+    else if (next_dtype == KESTREL_BF16) GN_LAUNCH_Q(__nv_bfloat16);
+    else return kestrel_fail(-2, "add_gated_normed: unknown dtype %d", next_dtype);
+#undef GN_LAUNCH_Q
+#undef GN_LAUNCH
     return kestrel_check_launch("add_gated_normed");
 }
 

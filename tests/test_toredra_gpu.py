@@ -324,6 +324,52 @@ def test_activation_in_the_products_epilogue(act, T_, N, K):
         _close(slices.float().cpu().numpy(), want, "bfloat16", f"{act} on slices", scale=max(1.0, float(np.abs(want).max())))
 
 
+@pytest.mark.parametrize("d", [520, 1024, 2056])
+def test_wide_rows_have_the_same_bits_in_steps_of_few_and_of_many_tokens(d):
+    """The kernels that take a row a block pick their thread count by the step's size, and the gates of the delta rule a
+    form of their own for few tokens; a row's bits must not move with either.  600 rows at once against the first 3 alone,
+    at widths that fold 2 and 4 virtual threads into one, products of 1, 3 and 9 slices; also against numpy."""
+    import torch
+    from kestrel_llm_b200.csrc import ops
+    rng = np.random.default_rng(d)
+    T_, few = 600, 3
+
+    def product(S, width, rows=T_):
+        return torch.from_numpy(rng.standard_normal((S, rows, width)).astype(np.float32)).to("cuda:0")
+
+    def vec(width, mean=0.0):
+        return torch.from_numpy((mean + rng.standard_normal(width)).astype(np.float32)).to("cuda:0")
+    y, g, a, b = product(9, d), product(3, d), product(1, d), product(9, d)
+    w, wn, wa, wb, yb, gb = vec(d, 1.0), vec(d, 1.0), vec(d, 1.0), vec(d, 1.0), vec(d), vec(d)
+    x0 = torch.from_numpy(rng.standard_normal((T_, d)).astype(np.float32)).to("cuda:0")
+    outs = {}
+    for rows in (T_, few):
+        x = x0[:rows].clone()
+        nxt = torch.empty((rows, d), dtype=torch.float32, device="cuda:0")
+        ops.add_gated_normed(x, ops.Partials(y[:, :rows].contiguous(), yb), ops.Partials(g[:, :rows].contiguous(), gb), w, 1e-6, wn, 1e-5, nxt)
+        c = ops.combine_normed(ops.Partials(a[:, :rows].contiguous()), wa, ops.Partials(b[:, :rows].contiguous()), wb, 1e-6, 0.5)
+        ops.raise_on_kernel_error()
+        outs[rows] = (x, nxt, c.data[0])
+    for many, alone in zip(outs[T_], outs[few]):
+        assert torch.equal(many[:few], alone)
+    ys = y.double().sum(0).cpu().numpy() + yb.double().cpu().numpy()
+    gs = g.double().sum(0).cpu().numpy() + gb.double().cpu().numpy()
+    z = ys / (1.0 + np.exp(-gs))
+    want = x0.double().cpu().numpy() + z / np.sqrt((z ** 2).mean(-1, keepdims=True) + 1e-6) * w.double().cpu().numpy()
+    _close(outs[T_][0].cpu().numpy(), want, "float32", "gated, normed, added")
+    _close(outs[T_][1].cpu().numpy(), want / np.sqrt((want ** 2).mean(-1, keepdims=True) + 1e-5) * wn.double().cpu().numpy(), "float32", "the next norm")
+    # the delta rule's gates: a head size for each form of the few-token kernel
+    for H, dh in ((3, 40), (2, 128), (2, 200)):
+        n = H * dh
+        fused, wz = product(3, 4 * n + 8), product(2, n)
+        ab, wb0 = vec(n), vec(n)
+        many = ops.removal_gates(ops.Partials(fused), 0, n, 2 * n, 3 * n, ab, ops.Partials(wz), wb0, 0.6, H, dh)
+        alone = ops.removal_gates(ops.Partials(fused[:, :few].contiguous()), 0, n, 2 * n, 3 * n, ab, ops.Partials(wz[:, :few].contiguous()), wb0, 0.6, H, dh)
+        ops.raise_on_kernel_error()
+        for m, o in zip(many, alone):
+            assert torch.equal(m[:few], o)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("scale,cap", [(1.0, 0.0), (2.5, 0.0), (1.0, 7.0), (0.3, 4.0)])
 def test_output_head_scales_then_caps(dtype, scale, cap):
