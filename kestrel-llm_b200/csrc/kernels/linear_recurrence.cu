@@ -278,6 +278,69 @@ recurrence_scan_kernel(const float *__restrict__ r, const float *__restrict__ w,
 #pragma unroll
                 for (int c = 0; c < LR_TC; ++c) out[((size_t)(tb + c) * H + h) * dv + j] = o[c];
             }
+        } else if (n == LR_TC && D <= 128) {
+            // With the correction the sum b^T S over a column's lanes lies on the way from state to state.  Two things keep
+            // the rest off that way: the next token's operands are in registers before this token's chain starts, and the
+            // previous token's read-out goes through the shuffle tree level by level beside this token's b^T S (the same
+            // tree as alone: same bits).
+            float4 K[M], R[M], W[M], A[M], B[M];
+            float vj = sv[jl];
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                K[m] = reinterpret_cast<const float4 *>(sk)[LR_LPC * m + part]; R[m] = reinterpret_cast<const float4 *>(sr)[LR_LPC * m + part];
+                W[m] = reinterpret_cast<const float4 *>(sw)[LR_LPC * m + part]; A[m] = reinterpret_cast<const float4 *>(sa)[LR_LPC * m + part];
+                B[m] = reinterpret_cast<const float4 *>(sb)[LR_LPC * m + part];
+            }
+            float o_prev = 0.f;
+#pragma unroll
+            for (int c = 0; c < LR_TC; ++c) {
+                float4 K2[M], R2[M], W2[M], A2[M], B2[M];
+                float v2 = 0.f;
+                if (c + 1 < LR_TC) {
+                    v2 = sv[(c + 1) * 32 + jl];
+#pragma unroll
+                    for (int m = 0; m < M; ++m) {
+                        const int e = (c + 1) * (D / 4) + LR_LPC * m + part;
+                        K2[m] = reinterpret_cast<const float4 *>(sk)[e]; R2[m] = reinterpret_cast<const float4 *>(sr)[e];
+                        W2[m] = reinterpret_cast<const float4 *>(sw)[e]; A2[m] = reinterpret_cast<const float4 *>(sa)[e];
+                        B2[m] = reinterpret_cast<const float4 *>(sb)[e];
+                    }
+                }
+                float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+                for (int m = 0; m < M; ++m) {
+                    s0 = fmaf(Sc[m][0], B[m].x, s0);
+                    s1 = fmaf(Sc[m][1], B[m].y, s1);
+                    s2 = fmaf(Sc[m][2], B[m].z, s2);
+                    s3 = fmaf(Sc[m][3], B[m].w, s3);
+                }
+                float held = (s0 + s1) + (s2 + s3);
+#pragma unroll
+                for (int sh = 1; sh < LR_LPC; sh <<= 1) {
+                    const float hx = __shfl_xor_sync(0xffffffffu, held, sh);
+                    const float ox = c > 0 ? __shfl_xor_sync(0xffffffffu, o_prev, sh) : 0.f;
+                    held += hx;
+                    if (c > 0) o_prev += ox;
+                }
+                if (c > 0 && live && part == 0) out[((size_t)(tb + c - 1) * H + h) * dv + j] = o_prev;
+                s0 = s1 = s2 = s3 = 0.f;
+#pragma unroll
+                for (int m = 0; m < M; ++m) {
+                    const float e0 = fmaf(A[m].x, held, K[m].x * vj), e1 = fmaf(A[m].y, held, K[m].y * vj);
+                    const float e2 = fmaf(A[m].z, held, K[m].z * vj), e3 = fmaf(A[m].w, held, K[m].w * vj);
+                    Sc[m][0] = fmaf(W[m].x, Sc[m][0], e0); s0 = fmaf(Sc[m][0], R[m].x, s0);
+                    Sc[m][1] = fmaf(W[m].y, Sc[m][1], e1); s1 = fmaf(Sc[m][1], R[m].y, s1);
+                    Sc[m][2] = fmaf(W[m].z, Sc[m][2], e2); s2 = fmaf(Sc[m][2], R[m].z, s2);
+                    Sc[m][3] = fmaf(W[m].w, Sc[m][3], e3); s3 = fmaf(Sc[m][3], R[m].w, s3);
+                }
+                o_prev = (s0 + s1) + (s2 + s3);
+                if (c + 1 < LR_TC) {
+                    vj = v2;
+#pragma unroll
+                    for (int m = 0; m < M; ++m) { K[m] = K2[m]; R[m] = R2[m]; W[m] = W2[m]; A[m] = A2[m]; B[m] = B2[m]; }
+                }
+            }
+            reduce_store(LR_TC - 1, o_prev);
         } else if (n == LR_TC) {
 #pragma unroll
             for (int c = 0; c < LR_TC; ++c) reduce_store(c, token(c));

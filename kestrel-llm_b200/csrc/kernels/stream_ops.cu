@@ -240,7 +240,7 @@ __device__ __forceinline__ float gn_block_sum(const float (&part)[Q], float *red
 // out[t] = mix * (a / sqrt(mean(a^2) + eps) * wa + b / sqrt(mean(b^2) + eps) * wb), float32.
 // ------------------------------------------------------------------------------------------
 template <int Q>
-__global__ void __launch_bounds__(GN_VT_MAX / Q)
+__global__ void __launch_bounds__(GN_VT_MAX / Q, 2 * Q)          // 2,048 threads an SM in every form
 combine_normed_kernel(const float *__restrict__ a, int Sa, size_t stride_a, const float *__restrict__ wa, const float *__restrict__ b, int Sb,
                       size_t stride_b, const float *__restrict__ wb, float eps, float mix, float *__restrict__ out, int d) {
     pdl_launch_dependents();
@@ -299,7 +299,7 @@ KESTREL_API int kestrel_combine_normed(const float *a, int Sa, long long stride_
 //     next_out[t] = residual[t] / sqrt(mean(residual[t]^2) + eps_next) * next_w       (storage type)
 // ------------------------------------------------------------------------------------------
 template <typename TOut, int Q>
-__global__ void __launch_bounds__(GN_VT_MAX / Q)
+__global__ void __launch_bounds__(GN_VT_MAX / Q, 2 * Q)          // 2,048 threads an SM in every form
 add_gated_normed_kernel(float *__restrict__ residual, const float *__restrict__ y, int Sy, size_t stride_y, const float *__restrict__ y_bias,
                         const float *__restrict__ g, int Sg, size_t stride_g, const float *__restrict__ g_bias, const float *__restrict__ w,
                         float eps, const float *__restrict__ next_w, float eps_next, TOut *__restrict__ next_out, int d) {
