@@ -387,7 +387,7 @@ __global__ void __launch_bounds__(AMG_THREADS)
 attention_merge_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml,
                        __nv_bfloat16 *__restrict__ out, const int *__restrict__ tile_seq,
                        const int *__restrict__ tile_row0, const int *__restrict__ cu_seqlens,
-                       int slices, int hd, int nq, int nkv) {
+                       int slices, int hd, int nq, int nkv, const float *__restrict__ sink) {
     pdl_launch_dependents();
     __shared__ float f_s[AMG_MAX_SLICES], lf_s[AMG_MAX_SLICES];
     __shared__ float red[AMG_THREADS / 32];
@@ -421,6 +421,8 @@ attention_merge_kernel(const float *__restrict__ part_o, const float *__restrict
     if (tid == 0) {             // the sum of the weights in ascending order, as the rows' own sums
         float L = 0.f;
         for (int s = 0; s < slices; ++s) L += lf_s[s];
+        // a softmax with one more term exp(sink[head]) that carries no value: entered once, here, against the rows' maximum
+        if (sink) L += exp2f(sink[qrow % nq] * 1.4426950408889634f - M);
         inv_l = L;
     }
     __syncthreads();
@@ -453,7 +455,7 @@ __global__ void __launch_bounds__(256)
 attention_merge_rows_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml,
                             __nv_bfloat16 *__restrict__ out, const int *__restrict__ tile_seq,
                             const int *__restrict__ tile_row0, const int *__restrict__ cu_seqlens,
-                            int slices, int hd, int nq, int nkv, int rows_per_tile) {
+                            int slices, int hd, int nq, int nkv, int rows_per_tile, const float *__restrict__ sink) {
     pdl_launch_dependents();
     const int tile = blockIdx.x, kvh = blockIdx.y, lane = threadIdx.x & 31;
     const int r = blockIdx.z * 8 + (threadIdx.x >> 5);
@@ -489,6 +491,7 @@ attention_merge_rows_kernel(const float *__restrict__ part_o, const float *__res
             }
         }
     }
+    if (sink) L += exp2f(sink[qrow % nq] * 1.4426950408889634f - M);      // the softmax's extra term, once, as in the kernel above
     if (d < hd) {
         __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x / L, acc.y / L), hi = __floats2bfloat162_rn(acc.z / L, acc.w / L);
         uint2 u2;
@@ -519,17 +522,17 @@ static int launch_attention(const AttnParams &p, int tiles, cudaStream_t stream)
 // attention_decode.cu and attention_tc.cu
 KESTREL_API int kestrel_attention_merge(const float *part_o, const float *part_ml, void *out, const int *tile_seq,
                                         const int *tile_row0, int tiles, int rows_per_tile, const int *cu_seqlens, int slices,
-                                        int hd, int nq, int nkv, cudaStream_t stream) {
+                                        int hd, int nq, int nkv, const float *sink, cudaStream_t stream) {
     KESTREL_REQUIRE(rows_per_tile >= 1 && rows_per_tile <= 65535, "attention_merge: tiles of %d rows", rows_per_tile);
     KESTREL_REQUIRE(slices >= 1 && slices <= AMG_MAX_SLICES, "attention_merge: %d slices; the kernel merges up to %d", slices, AMG_MAX_SLICES);
     KESTREL_REQUIRE(tiles <= 0x7fffffff && nkv <= 65535, "attention_merge: grid too large");
     if (rows_per_tile > 16 && slices <= AMW_MAX_SLICES && hd % 4 == 0 && hd <= 128 && (((uintptr_t)part_o | (uintptr_t)out) & 15) == 0) {
         kestrel_launch(attention_merge_rows_kernel, dim3(tiles, nkv, (rows_per_tile + 7) / 8), dim3(256), 0, stream, part_o, part_ml,
-                       (__nv_bfloat16 *)out, tile_seq, tile_row0, cu_seqlens, slices, hd, nq, nkv, rows_per_tile);
+                       (__nv_bfloat16 *)out, tile_seq, tile_row0, cu_seqlens, slices, hd, nq, nkv, rows_per_tile, sink);
         return kestrel_check_launch("attention_merge");
     }
     kestrel_launch(attention_merge_kernel, dim3(tiles, nkv, rows_per_tile), dim3(AMG_THREADS), 0, stream, part_o, part_ml, (__nv_bfloat16 *)out,
-                   tile_seq, tile_row0, cu_seqlens, slices, hd, nq, nkv);
+                   tile_seq, tile_row0, cu_seqlens, slices, hd, nq, nkv, sink);
     return kestrel_check_launch("attention_merge");
 }
 
@@ -582,7 +585,7 @@ KESTREL_API int kestrel_attention_mma(const void *q, const void *k_cache, const 
     if (rc) return rc;
     if (slices > 1) {
         KESTREL_REQUIRE(keys, "attention_mma: slices are merged for tiles of 16 rows only");
-        return kestrel_attention_merge(part_o, part_ml, out, tile_seq, tile_row0, tiles, 16, cu_seqlens, slices, hd, nq, nkv, stream);
+        return kestrel_attention_merge(part_o, part_ml, out, tile_seq, tile_row0, tiles, 16, cu_seqlens, slices, hd, nq, nkv, nullptr, stream);
     }
     return 0;
 }

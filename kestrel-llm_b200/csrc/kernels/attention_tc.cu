@@ -519,8 +519,9 @@ KESTREL_API int kestrel_attention_tc(const void *q, const void *k_cache, const v
                                        max_kv_ptr, scale, 0.f, nullptr, nullptr, nullptr, KESTREL_WEIGH_SOFTMAX, nullptr, stream);
 }
 
-// The same with a layer's options on the scores and on the weighing of keys (attention_score.cuh); with
-// options the key range is not cut into slices.
+// The same with a layer's options on the scores and on the weighing of keys (attention_score.cuh).  Softmax
+// weights may be cut into slices of keys (the extra term of "softmax_sink" then enters once, in the merge);
+// sigmoid weights take the key range in one slice.
 KESTREL_API int kestrel_attention_tc_scored(const void *q, const void *k_cache, const void *v_cache, void *out,
                                             float *part_o, float *part_ml, const int *tile_seq, const int *tile_row0,
                                             int tiles, int rows_per_tile, const int *cu_seqlens, const int *kv_lens, const int *block_table,
@@ -531,7 +532,8 @@ KESTREL_API int kestrel_attention_tc_scored(const void *q, const void *k_cache, 
     if (T == 0 || tiles == 0) return 0;
     const bool scored = softcap > 0.f || r1 != nullptr || weighting != KESTREL_WEIGH_SOFTMAX;
     KESTREL_REQUIRE(weighting >= 0 && weighting <= 2 && softcap >= 0.f && (r1 == nullptr) == (r2 == nullptr), "attention_tc: bad score options");
-    KESTREL_REQUIRE(!scored || slices == 1, "attention_tc: options on the scores go with one slice of keys, not %d", slices);
+    KESTREL_REQUIRE(!scored || slices == 1 || (weighting != KESTREL_WEIGH_SIGMOID && (weighting != KESTREL_WEIGH_SOFTMAX_SINK || sink)),
+                    "attention_tc: sigmoid weights, and an extra term without its numbers, go with one slice of keys, not %d", slices);
     KESTREL_REQUIRE(hd == AT_HD, "attention_tc: head size %d; this kernel is built for %d", hd, AT_HD);
     KESTREL_REQUIRE(rows_per_tile >= 1 && rows_per_tile <= 2 * AT_BM, "attention_tc: tiles of %d rows; a CTA takes up to %d", rows_per_tile, 2 * AT_BM);
     KESTREL_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_tc: %d query heads over %d kv heads", nq, nkv);
@@ -566,7 +568,8 @@ KESTREL_API int kestrel_attention_tc_scored(const void *q, const void *k_cache, 
     kestrel_launch(attention_tc_kernel, dim3((unsigned)((long long)tiles * nkv), 1, slices), dim3(AT_THREADS), smem, stream, map_k, map_v, p, cache_pages, rows_per_tile);
     rc = kestrel_check_launch("attention_tc");
     if (rc || slices == 1) return rc;
-    return kestrel_attention_merge(part_o, part_ml, out, tile_seq, tile_row0, tiles, rows_per_tile, cu_seqlens, slices, hd, nq, nkv, stream);
+    return kestrel_attention_merge(part_o, part_ml, out, tile_seq, tile_row0, tiles, rows_per_tile, cu_seqlens, slices, hd, nq, nkv,
+                                   scored && weighting == KESTREL_WEIGH_SOFTMAX_SINK ? sink : nullptr, stream);
 }
 
 // Error word of the kernel's bounded waits: 0 = none, else the number of the wait that gave up

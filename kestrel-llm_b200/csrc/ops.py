@@ -563,7 +563,7 @@ def attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
                  block_table: torch.Tensor, page_size: int, nq: int, nkv: int, hd: int, window: int, scale: float,
                  slices: int = 1, slice_len: int = 1 << 30, max_kv_dev: Optional[torch.Tensor] = None,
                  rows_per_tile: int = 128, score: Optional["ScoreOptions"] = None) -> None:
-    """tcgen05 attention of the listed tiles, head size 128 (with a layer's `ScoreOptions`, one slice): tiles of ``rows_per_tile`` rows, up
+    """tcgen05 attention of the listed tiles, head size 128 (with a layer's `ScoreOptions`; sigmoid weights in one slice): tiles of ``rows_per_tile`` rows, up
     to 256 (prompt portions; 16 for decode tokens); the key range may be cut into
     ``slices`` slices of ``slice_len`` keys (a multiple of 128) that are merged in ascending
     order; ``slices * slice_len`` must reach the longest request.  The cache tensors are

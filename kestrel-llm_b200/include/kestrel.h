@@ -275,7 +275,7 @@ KESTREL_API int kestrel_attention_plain(const void *q, const void *k_cache, cons
 KESTREL_API int kestrel_attention_mma(const void *q, const void *k_cache, const void *v_cache, void *out, float *part_o, float *part_ml, const int *tile_seq, const int *tile_row0, int tiles, int rows_per_tile, const int *cu_seqlens, const int *kv_lens, const int *block_table, int table_stride, int page_size, int T, int nq, int nkv, int hd, int window, int slices, int slice_len, const int *max_kv_ptr, float scale, kestrel_stream_t stream);
 KESTREL_API int kestrel_attention_mma_rows_per_tile(int hd);
 KESTREL_API int kestrel_attention_mma_slots(int hd);
-KESTREL_API int kestrel_attention_merge(const float *part_o, const float *part_ml, void *out, const int *tile_seq, const int *tile_row0, int tiles, int rows_per_tile, const int *cu_seqlens, int slices, int hd, int nq, int nkv, kestrel_stream_t stream);
+KESTREL_API int kestrel_attention_merge(const float *part_o, const float *part_ml, void *out, const int *tile_seq, const int *tile_row0, int tiles, int rows_per_tile, const int *cu_seqlens, int slices, int hd, int nq, int nkv, const float *sink, kestrel_stream_t stream);
 KESTREL_API int kestrel_attention_tc(const void *q, const void *k_cache, const void *v_cache, void *out, float *part_o, float *part_ml, const int *tile_seq, const int *tile_row0, int tiles, int rows_per_tile, const int *cu_seqlens, const int *kv_lens, const int *block_table, int table_width, int table_stride, int page_size, int cache_pages, int T, int nq, int nkv, int hd, int window, int slices, int slice_len, const int *max_kv_ptr, float scale, kestrel_stream_t stream);
 KESTREL_API int kestrel_attention_tc_supported(int hd, int page_size);
 KESTREL_API int kestrel_attention_tc_slots(void);

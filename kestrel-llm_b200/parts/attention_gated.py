@@ -25,7 +25,8 @@ are its own; ``out_bias``: whether the output projection has a bias (default: as
 Kernels: float32 and head sizes that are no multiples of 8 run on the plain kernel; bfloat16 on the
 ``mma.sync`` kernel of `ops.attention_window` (single-token steps share their keys out over CTAs),
 except steps with prompt portions of head size 128 without gate and kept tokens, which take the
-tcgen05 kernel (`ops.attention_tc`) with the same options.
+tcgen05 kernel (`ops.attention_tc`) with the same options; without a window it cuts a long key range
+into slices (softmax weights only) so that the request's last tile does not set the kernel's time.
 """
 from __future__ import annotations
 
@@ -41,6 +42,8 @@ from .linear import Linear
 class GatedWindowAttention(Mixer):
     force_plain = False        # tests: bfloat16 through the plain kernel too, the twin of the tensor-core one
     tcgen05 = True             # tests: off, portions of head size 128 stay on the mma.sync kernel
+    TC_SLICE = 512             # fewest keys a slice where a portion's key range is cut (softmax weights, no window)
+    TC_SLICE_FILL = 148        # CTAs that the cut should reach: one an SM
     TC_MIN_ROWS = 64           # a step whose longest portion has more rows (tokens x heads of a group) takes the tcgen05 kernel
     graph_safe = True          # forward launches kernels over device tensors of the batch only
 
@@ -148,8 +151,20 @@ class GatedWindowAttention(Mixer):
                 ops.attention_tc_supported(128, cache.page_size):
             # prompt portions of head size 128: the tcgen05 kernel, rows in tiles of 256 per request
             tile_seq, tile_row0 = ops.row_tiles(batch, G, 256)
+            # Few tiles far into a long context (a later portion of a long prompt) leave most SMs idle: softmax weights
+            # without a window then take the key range in slices, as many as fill the chip, merged in ascending order.
+            # A whole prompt has tiles enough and stays in one slice (cut at 512 keys, 2,048 tokens of 16 heads took 188
+            # instead of 171 us: the slices' float32 outputs and their merge cost more than the even load gains).
+            slices, slice_len = 1, 1 << 30
+            fill = self.TC_SLICE_FILL // max(1, int(tile_seq.shape[0]) * self.kv_heads)
+            if self.window == 0 and self.score.weighting != "sigmoid" and fill >= 2 and batch.max_kv_len > 2 * self.TC_SLICE and \
+                    (self.score.weighting != "softmax_sink" or self.score.sink is not None):
+                per = -(-batch.max_kv_len // min(32, fill))          # keys a slice if the chip is to be filled, in whole key tiles
+                slice_len = max(self.TC_SLICE, (per + 127) // 128 * 128)
+                slices = -(-batch.max_kv_len // slice_len)
             ops.attention_tc(q, cache.k, cache.v, a, tile_seq, tile_row0, batch.cu_seqlens, batch.kv_lens, table, cache.page_size, self.heads,
-                             self.kv_heads, 128, self.window, self.scale, rows_per_tile=256, score=score)
+                             self.kv_heads, 128, self.window, self.scale, slices=slices,
+                             slice_len=slice_len, rows_per_tile=256, score=score)
         elif self.dtype == torch.bfloat16 and not self.force_plain and \
                 ops.attention_window_supported(self.head_dim, self.v_head_dim, self.heads, self.kv_heads):
             ops.attention_window(q, cache.k, cache.v, batch, table, cache.page_size, a, self.heads, self.kv_heads, self.head_dim,

@@ -420,6 +420,35 @@ def test_portions_of_head_size_128_on_tcgen05(sizes, page, n, cuts):
     assert np.abs(fast - slow).max() <= 2e-2 * np.abs(want).max()
 
 
+@pytest.mark.parametrize("sizes,page,n,cuts,slice_len", [((8, 2, 128, 128), 16, 700, [300, 400], 128), ((4, 4, 128, 128), 32, 530, [530], 128),
+                                                         ((2, 1, 128, 128), 16, 900, [70, 500, 330], 256), ((4, 2, 128, 128), 16, 1500, [1500], 512)])
+def test_long_prompts_cut_their_keys_into_slices(sizes, page, n, cuts, slice_len):
+    """bfloat16: without a window the key range of few tiles far into a request is cut into slices on the tcgen05 kernel and
+    merged, each head's learned term entering once, in the merge (here forced for every portion): against the plain statement
+    and against the same portions in one slice."""
+    from kestrel_llm_b200.csrc import ops
+    from kestrel_llm_b200.parts import GatedWindowAttention
+    layer = _left(*sizes, scale=0.09, dims=64, base=10000.0, scaling=(8.0, 1.0, 4.0, 128))
+    seen = []
+    real, real_len, real_fill = ops.attention_tc, GatedWindowAttention.TC_SLICE, GatedWindowAttention.TC_SLICE_FILL
+
+    def noted(*a, **kw):
+        seen.append(kw.get("slices", 1))
+        return real(*a, **kw)
+    ops.attention_tc, GatedWindowAttention.TC_SLICE, GatedWindowAttention.TC_SLICE_FILL = noted, slice_len, 1 << 20
+    try:
+        cut, want, _ = _mixer_case(layer, "left", "bfloat16", page, n, cuts, seed=7, width=64)
+        ops.raise_on_kernel_error()
+        GatedWindowAttention.TC_SLICE = 1 << 20
+        whole, _, _ = _mixer_case(layer, "left", "bfloat16", page, n, cuts, seed=7, width=64)
+    finally:
+        ops.attention_tc, GatedWindowAttention.TC_SLICE, GatedWindowAttention.TC_SLICE_FILL = real, real_len, real_fill
+    ops.raise_on_kernel_error()
+    assert max(seen[:len(cuts)]) == -(-n // slice_len) and max(seen[len(cuts):]) == 1
+    _close(cut, want, "bfloat16", "attention in slices of keys")
+    assert np.abs(cut - whole).max() <= 1e-2 * np.abs(want).max()
+
+
 @pytest.mark.parametrize("sizes,n", [((4, 2, 64, 64), 420), ((8, 2, 32, 48), 500), ((3, 3, 128, 128), 200), ((24, 1, 32, 32), 300), ((6, 3, 96, 64), 700)])
 def test_single_token_steps_share_their_keys_out_over_ctas(sizes, n):
     """bfloat16: a step of single tokens cuts its keys into shares, a CTA each, merged by a second kernel that also adds
