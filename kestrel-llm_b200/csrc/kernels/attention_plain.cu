@@ -167,9 +167,24 @@ KESTREL_API int kestrel_attention_plain_scored(const void *q, const void *k_cach
                                                int keep_first, const float *gate, float scale, float softcap, const float *r1,
                                                const float *r2, const float *head_bias, int weighting, const float *sink,
                                                cudaStream_t stream) {
+    return kestrel_attention_plain_biased(q, k_cache, v_cache, positions, seq_of_token, block_table, table_stride, page_size, out, dtype, T, nq, nkv,
+                                          hd, vd, window, keep_first, gate, scale, softcap, r1, r2, head_bias, weighting, sink, nullptr, nullptr, 0,
+                                          stream);
+}
+
+// the same with a learned number per head and bucket of distances added to the scores: rel [buckets, nq], the bucket of
+// a distance from rel_bucket [rel_far + 1] (distances beyond rel_far share its bucket)
+KESTREL_API int kestrel_attention_plain_biased(const void *q, const void *k_cache, const void *v_cache,
+                                               const int *positions, const int *seq_of_token,
+                                               const int *block_table, int table_stride, int page_size,
+                                               void *out, int dtype, int T, int nq, int nkv, int hd, int vd, int window,
+                                               int keep_first, const float *gate, float scale, float softcap, const float *r1,
+                                               const float *r2, const float *head_bias, int weighting, const float *sink,
+                                               const float *rel, const int *rel_bucket, int rel_far, cudaStream_t stream) {
     if (T == 0) return 0;
     KESTREL_REQUIRE(weighting >= 0 && weighting <= 2 && softcap >= 0.f && (r1 == nullptr) == (r2 == nullptr), "attention_plain: bad score options");
-    const ScoreOpts opts = {softcap, r1, r2, head_bias, weighting, sink};
+    KESTREL_REQUIRE(!rel || (rel_bucket && rel_far >= 0), "attention_plain: a distance table without its buckets");
+    const ScoreOpts opts = {softcap, r1, r2, head_bias, weighting, sink, rel, rel_bucket, rel_far, nq};
     KESTREL_REQUIRE(T > 0 && nq > 0 && nkv > 0 && hd > 0 && vd > 0 && keep_first >= 0, "attention_plain: bad sizes");
     KESTREL_REQUIRE(hd <= 32 * PA_MAX_PER_LANE && vd <= 32 * PA_MAX_PER_LANE, "attention_plain: head size %d / %d exceeds %d", hd, vd, 32 * PA_MAX_PER_LANE);
     KESTREL_REQUIRE(nq <= 65535, "attention_plain: %d query heads exceed the grid", nq);

@@ -12,6 +12,8 @@
 //   `inv_freq` given: q and k (after their norm) are turned by position - pair j of a head's first `rot` dimensions
 //            by the angle position * inv_freq[j] (float32), `rot_mode` 0 pairing dimension j with j + rot / 2, 1 pairing
 //            2j with 2j + 1; `rot_scale` multiplies cos and sin; the rest of a head passes unchanged;
+//   `q_temp_every` > 0: q (after norm and rotation) times 1 + q_temp_coef * ln(floor((position + 1) / q_temp_every) + 1),
+//            a query temperature that grows with the position, in float32;
 //   q -> q_out in the storage type; k, v -> the token's slot in its request's pages;
 //   gate_out[t, h] = sigmoid(gate column h), float32.
 // One warp a head row (the blocks of a token share its head rows out), lanes over the head's
@@ -59,7 +61,7 @@ attn_prepare_ex_kernel(const float *__restrict__ partial, int S, size_t slice_st
                        const int *__restrict__ block_table, int table_stride, int page_size,
                        T *__restrict__ k_cache, T *__restrict__ v_cache, T *__restrict__ q_out, float *__restrict__ gate_out,
                        int nq, int nkv, int hd, int vd, int has_kv, const float *__restrict__ bias, int v_norm, int keep_x,
-                       const float *__restrict__ inv_freq, int rot, int rot_mode, float rot_scale) {
+                       const float *__restrict__ inv_freq, int rot, int rot_mode, float rot_scale, float q_temp_coef, int q_temp_every) {
     extern __shared__ float apx_ss[];              // qk_norm = 2: sum of squares of every q and k head, then (keep_x) their columns
     __shared__ float apx_rot[APX_WARPS][32 * APX_PER_LANE];   // rotate-half pairing: a warp's head, so that a lane reaches its partner
     pdl_launch_dependents();
@@ -94,6 +96,7 @@ attn_prepare_ex_kernel(const float *__restrict__ partial, int S, size_t slice_st
     }
     size_t slot_row = 0;
     const int pos = positions[t];
+    const float q_temp = q_temp_every > 0 ? 1.0f + q_temp_coef * logf((float)((pos + 1) / q_temp_every) + 1.0f) : 1.0f;
     if (has_kv) {
         const int page = block_table[(size_t)seq_of_token[t] * table_stride + pos / page_size];
         slot_row = (size_t)page * nkv * page_size + (pos % page_size);      // + kv head * page_size
@@ -119,6 +122,7 @@ attn_prepare_ex_kernel(const float *__restrict__ partial, int S, size_t slice_st
         for (int c = 0; c < APX_PER_LANE; ++c) ss = fmaf(x[c], x[c], ss);
         float mul = 1.f;
         const float *w = nullptr;
+        const float after = kind == 0 ? q_temp : 1.0f;
         if (kind != 2 && qk_norm == 1) {
             ss = warp_sum(ss);
             mul = 1.0f / sqrtf(ss / (float)n + eps);
@@ -166,7 +170,7 @@ attn_prepare_ex_kernel(const float *__restrict__ partial, int S, size_t slice_st
 #pragma unroll
         for (int c = 0; c < APX_PER_LANE; ++c) {
             const int i = lane + 32 * c;
-            if (i < n) dst[i] = from_f32<T>(x[c]);
+            if (i < n) dst[i] = from_f32<T>(q_temp_every > 0 ? x[c] * after : x[c]);
         }
     }
     if (gate_out && blockIdx.y == 0) {
@@ -195,7 +199,20 @@ KESTREL_API int kestrel_attn_prepare_rotated(const float *partial, int S, long l
                                              const int *block_table, int table_stride, int page_size, void *k_cache, void *v_cache,
                                              void *q_out, float *gate_out, int dtype, int T, int nq, int nkv, int hd, int vd, int has_kv,
                                              cudaStream_t stream) {
+    return kestrel_attn_prepare_tempered(partial, S, slice_stride, ld, bias, q_norm_w, k_norm_w, qk_norm, v_norm, norm_eps, inv_freq, rot, rot_mode,
+                                         rot_scale, 0.f, 0, positions, seq_of_token, block_table, table_stride, page_size, k_cache, v_cache, q_out,
+                                         gate_out, dtype, T, nq, nkv, hd, vd, has_kv, stream);
+}
+
+// the same with a query temperature: q times 1 + q_temp_coef * ln(floor((position + 1) / q_temp_every) + 1); q_temp_every = 0: none
+KESTREL_API int kestrel_attn_prepare_tempered(const float *partial, int S, long long slice_stride, int ld, const float *bias, const float *q_norm_w,
+                                              const float *k_norm_w, int qk_norm, int v_norm, float norm_eps, const float *inv_freq, int rot,
+                                              int rot_mode, float rot_scale, float q_temp_coef, int q_temp_every, const int *positions,
+                                              const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *k_cache,
+                                              void *v_cache, void *q_out, float *gate_out, int dtype, int T, int nq, int nkv, int hd, int vd,
+                                              int has_kv, cudaStream_t stream) {
     if (T == 0) return 0;
+    KESTREL_REQUIRE(q_temp_every >= 0, "attn_prepare_ex: a query temperature every %d positions", q_temp_every);
     KESTREL_REQUIRE(!inv_freq || (rot > 0 && rot % 2 == 0 && rot <= hd && (rot_mode == 0 || rot_mode == 1)),
                     "attn_prepare_ex: %d rotated dimensions of a head of %d (mode %d)", rot, hd, rot_mode);
     KESTREL_REQUIRE(qk_norm >= 0 && qk_norm <= 2, "attn_prepare_ex: qk_norm %d is none of 0, 1, 2", qk_norm);
@@ -213,11 +230,11 @@ KESTREL_API int kestrel_attn_prepare_rotated(const float *partial, int S, long l
     const int by = T >= 512 ? 1 : (n_heads + APX_WARPS - 1) / APX_WARPS;
     if (dtype == KESTREL_F32)
         kestrel_launch(attn_prepare_ex_kernel<float>, dim3(T, by), dim3(APX_WARPS * 32), smem, stream, partial, S, (size_t)slice_stride, ld, q_norm_w, k_norm_w, qk_norm, norm_eps,
-                       positions, seq_of_token, block_table, table_stride, page_size, (float *)k_cache, (float *)v_cache, (float *)q_out, gate_out, nq, nkv, hd, vd, has_kv, bias, v_norm, keep_x, inv_freq, rot, rot_mode, rot_scale);
+                       positions, seq_of_token, block_table, table_stride, page_size, (float *)k_cache, (float *)v_cache, (float *)q_out, gate_out, nq, nkv, hd, vd, has_kv, bias, v_norm, keep_x, inv_freq, rot, rot_mode, rot_scale, q_temp_coef, q_temp_every);
     else if (dtype == KESTREL_BF16)
         kestrel_launch(attn_prepare_ex_kernel<__nv_bfloat16>, dim3(T, by), dim3(APX_WARPS * 32), smem, stream, partial, S, (size_t)slice_stride, ld, q_norm_w, k_norm_w, qk_norm, norm_eps,
                        positions, seq_of_token, block_table, table_stride, page_size, (__nv_bfloat16 *)k_cache, (__nv_bfloat16 *)v_cache, (__nv_bfloat16 *)q_out, gate_out, nq, nkv,
-                       hd, vd, has_kv, bias, v_norm, keep_x, inv_freq, rot, rot_mode, rot_scale);
+                       hd, vd, has_kv, bias, v_norm, keep_x, inv_freq, rot, rot_mode, rot_scale, q_temp_coef, q_temp_every);
     else
         return kestrel_fail(-2, "attn_prepare_ex: unknown dtype %d", dtype);
     return kestrel_check_launch("attn_prepare_ex");

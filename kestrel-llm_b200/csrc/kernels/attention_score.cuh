@@ -3,6 +3,8 @@
 //
 //   s <- cap * tanh(s / cap)                      if cap > 0
 //   s <- s - r1[head] * ln(1 + r2[head] * (i - j))   if r1 is given (i the query's position, j the key's)
+//   s <- s + rel[bucket[min(i - j, far)], head]   if rel is given: a learned number per head and bucket of distances;
+//                the buckets of the distances 0 .. far come as a table (every distance beyond far shares far's)
 //   weighting 0: softmax over the visible keys
 //             1: softmax with one more term in the denominator that carries no value: exp(sink[head]) where a
 //                layer has learned numbers for it, exp(0) otherwise
@@ -20,6 +22,9 @@ struct ScoreOpts {
     const float *head_bias;    // [nq] or null; read by weighting 2 only
     int weighting;
     const float *sink;         // [nq] or null (= zeros); read by weighting 1 only
+    const float *rel;          // [buckets, rel_heads] or null
+    const int *rel_bucket;     // [rel_far + 1]: bucket of a distance
+    int rel_far, rel_heads;
 };
 
 // the options of one head, fetched once
@@ -27,7 +32,15 @@ struct HeadScore {
     float cap, inv_cap, r1, r2, bias;
     float sink;                // the extra term's exponent (weighting 1), as the scores are: not in base-2 units
     bool dist;
+    const float *rel;          // this head's column of the distance table, or null
+    const int *rel_bucket;
+    int rel_far, rel_heads;
+    __device__ __forceinline__ float rel_of(int distance) const { return rel[(size_t)rel_bucket[min(distance, rel_far)] * rel_heads]; }
     __device__ __forceinline__ HeadScore(const ScoreOpts &o, int head) {
+        rel = o.rel ? o.rel + head : nullptr;
+        rel_bucket = o.rel_bucket;
+        rel_far = o.rel_far;
+        rel_heads = o.rel_heads;
         cap = o.softcap;
         inv_cap = o.softcap > 0.f ? 1.0f / o.softcap : 0.f;
         dist = o.r1 != nullptr;
@@ -40,6 +53,7 @@ struct HeadScore {
     __device__ __forceinline__ float operator()(float s, int distance) const {
         if (cap > 0.f) s = cap * tanhf(s * inv_cap);
         if (dist) s -= r1 * logf(1.0f + r2 * (float)distance);
+        if (rel) s += rel_of(distance);
         return s + bias;
     }
     // The same on the special-function unit, for the tensor-core kernels (their P is rounded to bfloat16
@@ -48,6 +62,7 @@ struct HeadScore {
     __device__ __forceinline__ float fast(float s, int distance) const {
         if (cap > 0.f) s = fmaf(-2.0f * cap, score_rcp(1.0f + score_exp2(s * (inv_cap * 2.8853900817779268f))), cap);
         if (dist) s -= r1 * __logf(fmaf(r2, (float)distance, 1.0f));
+        if (rel) s += rel_of(distance);
         return s + bias;
     }
     // The same with the layer's options as compile-time facts, for loops over many scores: nothing of an option that

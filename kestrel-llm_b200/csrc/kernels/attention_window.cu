@@ -457,6 +457,18 @@ KESTREL_API int kestrel_attention_window_scored(const void *q, const void *k_cac
                                                 int nseq, int max_count, int nq, int nkv, int hd, int vd, int window, int keep_first, float scale,
                                                 float softcap, const float *r1, const float *r2, const float *head_bias, int weighting,
                                                 const float *sink, int ksplit, float *scratch, cudaStream_t stream) {
+    return kestrel_attention_window_biased(q, k_cache, v_cache, out, gate, cu_seqlens, kv_lens, block_table, table_stride, page_size, nseq, max_count,
+                                           nq, nkv, hd, vd, window, keep_first, scale, softcap, r1, r2, head_bias, weighting, sink, nullptr, nullptr, 0,
+                                           ksplit, scratch, stream);
+}
+
+// the same with a learned number per head and bucket of distances added to the scores (ScoreOpts.rel)
+KESTREL_API int kestrel_attention_window_biased(const void *q, const void *k_cache, const void *v_cache, void *out, const float *gate,
+                                                const int *cu_seqlens, const int *kv_lens, const int *block_table, int table_stride, int page_size,
+                                                int nseq, int max_count, int nq, int nkv, int hd, int vd, int window, int keep_first, float scale,
+                                                float softcap, const float *r1, const float *r2, const float *head_bias, int weighting,
+                                                const float *sink, const float *rel, const int *rel_bucket, int rel_far, int ksplit,
+                                                float *scratch, cudaStream_t stream) {
     if (nseq == 0 || max_count == 0) return 0;
     KESTREL_REQUIRE(ksplit >= 1 && ksplit <= 65535 && (ksplit == 1 || scratch), "attention_window: %d shares of the keys without scratch", ksplit);
     KESTREL_REQUIRE(weighting >= 0 && weighting <= 2 && softcap >= 0.f && (r1 == nullptr) == (r2 == nullptr), "attention_window: bad score options");
@@ -481,8 +493,9 @@ KESTREL_API int kestrel_attention_window_scored(const void *q, const void *k_cac
     p.keep_first = window > 0 ? keep_first : 0;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.scale = scale;
-    p.opts = {softcap, r1, r2, head_bias, weighting, sink};
-    p.scored = softcap > 0.f || r1 != nullptr || weighting != KESTREL_WEIGH_SOFTMAX;
+    KESTREL_REQUIRE(!rel || (rel_bucket && rel_far >= 0), "attention_window: a distance table without its buckets");
+    p.opts = {softcap, r1, r2, head_bias, weighting, sink, rel, rel_bucket, rel_far, nq};
+    p.scored = softcap > 0.f || r1 != nullptr || rel != nullptr || weighting != KESTREL_WEIGH_SOFTMAX;
     const int D = max(hd, vd), G = nq / nkv;
     const bool keys_mode = (long long)max_count * G <= AW_KEYS_MODE_ROWS;
     if (!keys_mode) ksplit = 1;

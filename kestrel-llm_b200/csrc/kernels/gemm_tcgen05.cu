@@ -34,9 +34,11 @@ enum { TC_PARTIAL = 0, TC_SWIGLU = 1, TC_PARTIAL2 = 2, TC_SWIGLU_T = 3, TC_QKV_P
 // ACT (CTA pairs only): the PARTIAL product whose epilogue applies an activation to the accumulator
 // and writes the storage type, out bf16 [T, N] = act(x w^T) - a feed-forward's first product without
 // a gate: the float32 plane is neither written nor read back.  The kernel's `up_row_offset` argument
-// carries the activation: 1 the square of relu, 2 tanh, 3 silu (the numbering and the arithmetic of
+// carries the activation: 1 the square of relu, 2 tanh, 3 silu, 4 gelu (erf), 5 gelu (tanh form) (the numbering and the arithmetic of
 // the elementwise kernel that serves the product when it comes as slices: same bits).
 __device__ __forceinline__ float tc_act(float z, int act) {
+    if (act == 4) return 0.5f * z * (1.0f + erff(z * 0.7071067811865476f));
+    if (act == 5) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
     if (act == 1) { const float r = fmaxf(z, 0.f); return r * r; }
     if (act == 2) return tanhf(z);
     if (act == 3) return z / (1.0f + expf(-z));
@@ -1140,7 +1142,7 @@ KESTREL_API int kestrel_gemm_tc_add(const void *x, const void *w, float *residua
 KESTREL_API int kestrel_gemm_tc_act(const void *x, const void *w, void *out, int act, int T, int N, int K, long long ldx, long long ldw,
                                     long long ldo, cudaStream_t stream) {
     if (T == 0) return 0;
-    KESTREL_REQUIRE(act >= 1 && act <= 3, "gemm_tc_act: unknown activation %d", act);
+    KESTREL_REQUIRE(act >= 1 && act <= 5, "gemm_tc_act: unknown activation %d", act);
     if (T <= g_pair_min_tokens || !g_persistent || !g_pairs || !kestrel_gemm_tc_supported(x, w, T, N, K, ldx, ldw)) return 1;
     if (kestrel_gemm_tc_splits(T, N, K) > 1) return 1;
     CUtensorMap mw, mx;

@@ -67,6 +67,90 @@ KESTREL_API int kestrel_moe_route(const float *z_part, int S, long long slice_st
     return kestrel_check_launch("moe_route");
 }
 
+// A router of another kind: scores s = sigmoid(z); the experts are CHOSEN by s + correction[e] (a number per expert that
+// steers the load), but weighted by s alone.  The experts form `n_groups` equal groups of neighbours; a group's score is
+// the sum of its two largest choice scores (its only one where a group is one expert), and only experts of the `keep`
+// best groups can be chosen.  Weights: the chosen experts' s divided by their sum (+ 1e-20), times `scale`.  Among equal
+// scores the lowest index wins.  A warp a token; all float32.
+__device__ __forceinline__ void warp_argmax(float &best, int &arg) {
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+        if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+    }
+}
+
+__global__ void __launch_bounds__(32)
+moe_route_sigmoid_kernel(const float *__restrict__ z_part, int S, size_t slice_stride, const float *__restrict__ correction, int E, int top,
+                         int n_groups, int keep, float scale, int *__restrict__ ids, float *__restrict__ weights) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float rs[];
+    float *s = rs, *choice = rs + E, *gs = rs + 2 * E;          // s [E], choice [E], gs [n_groups]
+    const int t = blockIdx.x, lane = threadIdx.x;
+    for (int e = lane; e < E; e += 32) {
+        const float z = sum_slices(z_part, S, slice_stride, (size_t)t * E + e);
+        s[e] = 1.0f / (1.0f + expf(-z));
+        choice[e] = s[e] + (correction ? correction[e] : 0.f);
+    }
+    __syncwarp();
+    if (n_groups > 1 && keep < n_groups) {
+        const int per = E / n_groups;
+        for (int g = lane; g < n_groups; g += 32) {
+            float a = -INFINITY, b = -INFINITY;                   // the two largest, a >= b
+            for (int e = g * per; e < (g + 1) * per; ++e) {
+                const float v = choice[e];
+                if (v > a) { b = a; a = v; }
+                else if (v > b) b = v;
+            }
+            gs[g] = per > 1 ? a + b : a;
+        }
+        __syncwarp();
+        // the groups that stay are marked by +inf; then every expert of another group is closed
+        for (int k = 0; k < keep; ++k) {
+            float best = -INFINITY;
+            int arg = 0x7fffffff;
+            for (int g = lane; g < n_groups; g += 32)
+                if (gs[g] != INFINITY && (gs[g] > best || arg == 0x7fffffff)) { best = gs[g]; arg = g; }
+            warp_argmax(best, arg);
+            if (lane == 0 && arg != 0x7fffffff) gs[arg] = INFINITY;
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32)
+            if (gs[e / per] != INFINITY) choice[e] = -INFINITY;
+        __syncwarp();
+    }
+    float mine = 0.f;                                  // lane k keeps the k-th chosen expert's score s
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        for (int e = lane; e < E; e += 32)
+            if (choice[e] > best) { best = choice[e]; arg = e; }
+        warp_argmax(best, arg);
+        if (arg == 0x7fffffff) arg = 0;               // fewer open experts than `top`: never with keep * (E / n_groups) >= top
+        if (lane == 0) ids[(size_t)t * top + k] = arg;
+        if (lane == k % 32) mine = s[arg];
+        __syncwarp();
+        if (lane == 0) choice[arg] = -INFINITY;
+        __syncwarp();
+    }
+    float denom = lane < top ? mine : 0.f;
+    for (int o = 16; o > 0; o >>= 1) denom += __shfl_xor_sync(0xffffffffu, denom, o);
+    if (lane < top) weights[(size_t)t * top + lane] = mine / (denom + 1e-20f) * scale;
+}
+
+KESTREL_API int kestrel_moe_route_sigmoid(const float *z_part, int S, long long slice_stride, const float *correction, int n_groups, int keep,
+                                          float scale, int *ids, float *weights, int T, int E, int top, cudaStream_t stream) {
+    if (T == 0) return 0;
+    KESTREL_REQUIRE(T > 0 && E > 0 && top > 0 && top <= E && top <= 32 && S > 0, "moe_route_sigmoid: bad sizes E=%d top=%d", E, top);
+    KESTREL_REQUIRE(E <= 4096, "moe_route_sigmoid: %d experts exceed 4096", E);
+    KESTREL_REQUIRE(n_groups >= 1 && E % n_groups == 0 && keep >= 1 && keep <= n_groups && (long long)keep * (E / n_groups) >= top,
+                    "moe_route_sigmoid: %d groups of %d experts, %d kept, %d chosen", n_groups, E, keep, top);
+    kestrel_launch(moe_route_sigmoid_kernel, dim3(T), dim3(32), (size_t)(2 * E + n_groups) * sizeof(float), stream, z_part, S, (size_t)slice_stride,
+                   correction, E, top, n_groups, keep, scale, ids, weights);
+    return kestrel_check_launch("moe_route_sigmoid");
+}
+
 // ------------------------------------------------------------------------------------------
 // One block groups the P = T * top pairs by expert.
 //   offsets [E + 1]; row_pair [P]: pair of sorted row r; pair_row [P]: sorted row of a pair;
@@ -133,6 +217,15 @@ KESTREL_API int kestrel_moe_max_tiles(int P, int E, int rows_per_tile) { return 
 #define MP_BM 64
 #define MP_BN 64
 #define MP_BK 16
+
+// activations of an expert without a gate, y = W_down act(W_up x): 1 the exact gelu (erf), 2 its tanh form, 3 silu, 4 relu squared
+__device__ __forceinline__ float expert_up_act(float z, int kind) {
+    if (kind == 1) return 0.5f * z * (1.0f + erff(z * 0.7071067811865476f));
+    if (kind == 2) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    if (kind == 3) return z / (1.0f + expf(-z));
+    const float r = fmaxf(z, 0.f);
+    return r * r;
+}
 
 __device__ __forceinline__ float expert_act(float g, float u, float limit) {
     g = fminf(g, limit);
@@ -210,13 +303,15 @@ moe_gemm_plain_kernel(const T *__restrict__ x, long long ldx, const T *__restric
     for (int i = 0; i < 4; ++i) {
         const int r = ty * 4 + i;
         if (r >= rows) continue;
-        const float pw = GATE_UP ? 0.f : pair_weight[row_pair[r0 + r]];
+        const float pw = (GATE_UP || !pair_weight) ? 0.f : pair_weight[row_pair[r0 + r]];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
             if (n >= N) continue;
             if (GATE_UP)
                 ((T *)out)[(size_t)(r0 + r) * ldo + n] = from_f32<T>(expert_act(acc[0][i][j], acc[GATE_UP ? 1 : 0][i][j], limit));
+            else if (!pair_weight)          // an up product: the activation `limit` names, in the storage type
+                ((T *)out)[(size_t)(r0 + r) * ldo + n] = from_f32<T>(expert_up_act(acc[0][i][j], (int)limit));
             else
                 ((float *)out)[(size_t)(r0 + r) * ldo + n] = acc[0][i][j] * pw;
         }
@@ -349,6 +444,15 @@ moe_gemm_mma_kernel(const __nv_bfloat16 *__restrict__ x, long long ldx, const __
                     const int f = n0 + j * 8 + 2 * tq + c;
                     if (f < N) o[f] = __float2bfloat16_rn(expert_act(acc[j][2 * half + c], acc[j + 8][2 * half + c], limit));
                 }
+        } else if (!pair_weight) {          // an up product: the activation `limit` names, in the storage type
+            __nv_bfloat16 *o = (__nv_bfloat16 *)out + (size_t)(r0 + r) * ldo;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int f = n0 + j * 8 + 2 * tq + c;
+                    if (f < N) o[f] = __float2bfloat16_rn(expert_up_act(acc[j][2 * half + c], (int)limit));
+                }
         } else {
             const float pw = pair_weight[row_pair[r0 + r]];
             float *o = (float *)out + (size_t)(r0 + r) * ldo;
@@ -423,6 +527,53 @@ KESTREL_API int kestrel_moe_down(const void *act, const void *w, const int *offs
     else
         return kestrel_fail(-2, "moe_down: unknown dtype %d", dtype);
     return kestrel_check_launch("moe_down");
+}
+
+// Experts without a gate: act [P, ff] = activation(W_up[e] xs) in the storage type, xs [P, K] the pairs' input rows gathered in
+// sorted order, w [E, ff, K]; `act_kind` 1 exact gelu (erf), 2 gelu in its tanh form, 3 silu, 4 relu squared
+KESTREL_API int kestrel_moe_up_act(const void *xs, const void *w, const int *offsets, const int *row_pair, const int *tile_expert,
+                                   const int *tile_row0, const int *n_tiles, int max_tiles, int act_kind, void *act, int dtype, int ff, int K,
+                                   cudaStream_t stream) {
+    if (max_tiles == 0) return 0;
+    KESTREL_REQUIRE(max_tiles > 0 && max_tiles <= 65535 && ff > 0 && K > 0 && act_kind >= 1 && act_kind <= 4, "moe_up_act: bad sizes or activation %d", act_kind);
+    dim3 grid((ff + MP_BN - 1) / MP_BN, max_tiles);
+    const float kind = (float)act_kind;
+    if (dtype == KESTREL_F32)
+        kestrel_launch(moe_gemm_plain_kernel<float, false>, grid, dim3(256), 0, stream, (const float *)xs, (long long)K, (const float *)w, (long long)ff * K, (long long)K,
+                       offsets, row_pair, tile_expert, tile_row0, n_tiles, 1, (const float *)nullptr, kind, act, (long long)ff, ff, K);
+    else if (dtype == KESTREL_BF16 && moe_mma_takes(xs, (long long)K, w, K)) {
+        moe_mma_attr<false>();
+        kestrel_launch(moe_gemm_mma_kernel<false>, dim3((ff + MM_BN - 1) / MM_BN, max_tiles), dim3(128), MM_SMEM, stream, (const __nv_bfloat16 *)xs, (long long)K,
+                       (const __nv_bfloat16 *)w, (long long)ff * K, (long long)K, offsets, row_pair, tile_expert, tile_row0, n_tiles, 1, (const float *)nullptr, kind, act,
+                       (long long)ff, ff, K);
+    } else if (dtype == KESTREL_BF16)
+        kestrel_launch(moe_gemm_plain_kernel<__nv_bfloat16, false>, grid, dim3(256), 0, stream, (const __nv_bfloat16 *)xs, (long long)K, (const __nv_bfloat16 *)w,
+                       (long long)ff * K, (long long)K, offsets, row_pair, tile_expert, tile_row0, n_tiles, 1, (const float *)nullptr, kind, act, (long long)ff, ff, K);
+    else
+        return kestrel_fail(-2, "moe_up_act: unknown dtype %d", dtype);
+    return kestrel_check_launch("moe_up_act");
+}
+
+// xs[r, :] = x[row_pair[r] / top, :] in any storage type
+template <typename T>
+__global__ void moe_gather_rows_any_kernel(const T *__restrict__ x, long long ldx, const int *__restrict__ row_pair, int top, T *__restrict__ xs, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const T *src = x + (size_t)(row_pair[r] / top) * ldx;
+    for (int i = threadIdx.x; i < K; i += blockDim.x) xs[(size_t)r * K + i] = src[i];
+}
+
+KESTREL_API int kestrel_moe_gather_rows_any(const void *x, long long ldx, const int *row_pair, int top, void *xs, int dtype, int P, int K, cudaStream_t stream) {
+    if (P == 0) return 0;
+    KESTREL_REQUIRE(P > 0 && K > 0 && top > 0, "moe_gather_rows: bad sizes");
+    if (dtype == KESTREL_F32)
+        kestrel_launch(moe_gather_rows_any_kernel<float>, dim3(P), dim3(128), 0, stream, (const float *)x, ldx, row_pair, top, (float *)xs, K);
+    else if (dtype == KESTREL_BF16)
+        kestrel_launch(moe_gather_rows_any_kernel<__nv_bfloat16>, dim3(P), dim3(128), 0, stream, (const __nv_bfloat16 *)x, ldx, row_pair, top, (__nv_bfloat16 *)xs, K);
+    else
+        return kestrel_fail(-2, "moe_gather_rows: unknown dtype %d", dtype);
+    return kestrel_check_launch("moe_gather_rows");
 }
 
 // out[t, n] = sum_k y[pair_row[t * top + k], n], k ascending

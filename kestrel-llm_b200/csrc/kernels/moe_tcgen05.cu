@@ -137,6 +137,22 @@ moe_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__
                                 o[(size_t)(t0 + c + j) * ldo + n] = __float2bfloat16_rn(gg * (1.0f / (1.0f + expf(-1.702f * gg))) * (uu + 1.0f));
                             }
                     }
+                } else if (!pair_weight) {          // an up product of experts without a gate: the activation `limit` names
+                    __nv_bfloat16 *o = (__nv_bfloat16 *)out;
+                    const int kind = (int)limit;
+                    if (n < N) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (c + j < valid) {
+                                const float z = g[j];
+                                float a;
+                                if (kind == 1) a = 0.5f * z * (1.0f + erff(z * 0.7071067811865476f));
+                                else if (kind == 2) a = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+                                else if (kind == 3) a = z / (1.0f + expf(-z));
+                                else a = fmaxf(z, 0.f) * fmaxf(z, 0.f);
+                                o[(size_t)(t0 + c + j) * ldo + n] = __float2bfloat16_rn(a);
+                            }
+                    }
                 } else {
                     float *o = (float *)out;
                     // the 16 rows' routing weights: lane j fetches row j's, the others get it by shuffle
@@ -220,6 +236,18 @@ KESTREL_API int kestrel_moe_down_tc(const void *act, const void *w, const int *o
     if (rc == 0) rc = kestrel_tensor_map_bf16(&mx, act, P, ff, ff, MT_BN);
     if (rc != 0) return rc;
     return moe_tc_launch<false>(mw, mx, (void *)y, offsets, row_pair, tile_expert, tile_row0, n_tiles, max_tiles, pair_weight, 0.f, N, 0, N, ff, N, stream);
+}
+
+// xs [P, K] rows sorted by expert; w [E, ff, K]; act [P, ff] bfloat16 = activation(W_up[e] xs) of experts without a gate
+KESTREL_API int kestrel_moe_up_act_tc(const void *xs, const void *w, const int *offsets, const int *tile_expert, const int *tile_row0,
+                                      const int *n_tiles, int max_tiles, int act_kind, void *act, int P, int E, int ff, int K, cudaStream_t stream) {
+    if (P == 0) return 0;
+    KESTREL_REQUIRE(P > 0 && E > 0 && ff > 0 && K > 0 && max_tiles > 0 && max_tiles <= 65535 && act_kind >= 1 && act_kind <= 4, "moe_up_act_tc: bad sizes");
+    CUtensorMap mw, mx;
+    int rc = kestrel_tensor_map_bf16(&mw, w, (long long)E * ff, K, K, MT_BM);
+    if (rc == 0) rc = kestrel_tensor_map_bf16(&mx, xs, P, K, K, MT_BN);
+    if (rc != 0) return rc;
+    return moe_tc_launch<false>(mw, mx, act, offsets, nullptr, tile_expert, tile_row0, n_tiles, max_tiles, nullptr, (float)act_kind, ff, 0, ff, K, ff, stream);
 }
 
 // xs[r, :] = x[row_pair[r] / top, :], 16 bytes a thread and step

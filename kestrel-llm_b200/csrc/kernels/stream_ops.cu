@@ -169,9 +169,11 @@ KESTREL_API int kestrel_partial_columns(const float *p, int S, long long slice_s
 }
 
 // ------------------------------------------------------------------------------------------
-// The same with an activation on the summed columns: 0 none, 1 the square of relu, 2 tanh, 3 silu.
+// The same with an activation on the summed columns: 0 none, 1 the square of relu, 2 tanh, 3 silu, 4 gelu (erf), 5 gelu (tanh form).
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ float column_act(float z, int act) {
+    if (act == 4) return 0.5f * z * (1.0f + erff(z * 0.7071067811865476f));                                   // the exact gelu
+    if (act == 5) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));       // its tanh form
     if (act == 1) { const float r = fmaxf(z, 0.f); return r * r; }
     if (act == 2) return tanhf(z);
     if (act == 3) return z / (1.0f + expf(-z));
@@ -195,7 +197,7 @@ __global__ void partial_columns_act_kernel(const float *__restrict__ p, int S, s
 KESTREL_API int kestrel_partial_columns_act(const float *p, int S, long long slice_stride, int ld, int col0, const float *bias, int act, void *out,
                                             int dtype, int T, int n, cudaStream_t stream) {
     if (T == 0) return 0;
-    KESTREL_REQUIRE(T > 0 && n > 0 && S > 0 && col0 >= 0 && col0 + n <= ld && act >= 0 && act <= 3, "partial_columns_act: bad sizes or activation %d", act);
+    KESTREL_REQUIRE(T > 0 && n > 0 && S > 0 && col0 >= 0 && col0 + n <= ld && act >= 0 && act <= 5, "partial_columns_act: bad sizes or activation %d", act);
     size_t total = (size_t)T * n;
     unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == KESTREL_F32)
@@ -405,4 +407,116 @@ KESTREL_API int kestrel_logit_scale_cap(float *logits, long long ld, int R, int 
     KESTREL_REQUIRE(R > 0 && V > 0 && cap >= 0.f, "logit_scale_cap: bad sizes R=%d V=%d", R, V);
     kestrel_launch(logit_scale_cap_kernel, dim3((V + 255) / 256, R < 32768 ? R : 32768), dim3(256), 0, stream, logits, (size_t)ld, R, V, scale, cap);
     return kestrel_check_launch("logit_scale_cap");
+}
+
+// ------------------------------------------------------------------------------------------
+// residual[t] += sum_s a[s, t] + sum_s b[s, t] + sum_s c[s, t]  (b and c may be null): `add_two` with one more
+// product, for a layer whose feed-forward is two (routed experts and one that every token takes).  The order of
+// the sum is fixed: (a + b) + c, each its slices in ascending order; without c the bits of `add_two`.
+// ------------------------------------------------------------------------------------------
+template <typename TOut>
+__global__ void add_three_kernel(float *__restrict__ residual, const float *__restrict__ a, int Sa, size_t stride_a,
+                                 const float *__restrict__ b, int Sb, size_t stride_b, const float *__restrict__ c, int Sc, size_t stride_c,
+                                 TOut *__restrict__ cast, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    const float va = sum_slices(a, Sa, stride_a, idx), vb = Sb > 0 ? sum_slices(b, Sb, stride_b, idx) : 0.f;
+    float add = va + vb;
+    if (Sc > 0) add += sum_slices(c, Sc, stride_c, idx);
+    float v = residual[idx] + add;
+    residual[idx] = v;
+    if (cast) cast[idx] = from_f32<TOut>(v);
+}
+
+KESTREL_API int kestrel_add_three(float *residual, const float *a, int Sa, long long stride_a, const float *b, int Sb, long long stride_b,
+                                  const float *c, int Sc, long long stride_c, void *cast, int cast_dtype, int T, int d, cudaStream_t stream) {
+    if (T == 0) return 0;
+    KESTREL_REQUIRE(T > 0 && d > 0 && a && Sa > 0 && (b || Sb == 0) && (c || Sc == 0), "add_three: bad arguments");
+    size_t n = (size_t)T * d;
+    unsigned blocks = (unsigned)((n + 255) / 256);
+    if (cast_dtype == KESTREL_F32)
+        kestrel_launch(add_three_kernel<float>, dim3(blocks), dim3(256), 0, stream, residual, a, Sa, (size_t)stride_a, b, Sb, (size_t)stride_b, c, Sc, (size_t)stride_c, (float *)cast, n);
+    else if (cast_dtype == KESTREL_BF16)
+        kestrel_launch(add_three_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, residual, a, Sa, (size_t)stride_a, b, Sb, (size_t)stride_b, c, Sc, (size_t)stride_c, (__nv_bfloat16 *)cast, n);
+    else
+        return kestrel_fail(-2, "add_three: unknown dtype %d", cast_dtype);
+    return kestrel_check_launch("add_three");
+}
+
+// ------------------------------------------------------------------------------------------
+// x[t, i] *= sigmoid(sum_s g[s, t, col0 + i] + bias[col0 + i]), i < n, in place in the storage type: a gate per element of a
+// mixer's output, its logits columns of a product of the mixer's input.  The sigmoid is float32.
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void gate_columns_mul_kernel(T *__restrict__ x, const float *__restrict__ g, int S, size_t slice_stride, int ld, int col0,
+                                        const float *__restrict__ bias, int n, size_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    size_t t = idx / n;
+    int i = (int)(idx % n);
+    float z = sum_slices(g, S, slice_stride, t * ld + col0 + i);
+    if (bias) z += bias[col0 + i];
+    x[idx] = from_f32<T>(to_f32<T>(x[idx]) * (1.0f / (1.0f + expf(-z))));
+}
+
+KESTREL_API int kestrel_gate_columns_mul(void *x, int dtype, const float *g, int S, long long slice_stride, int ld, int col0, const float *bias,
+                                         int T, int n, cudaStream_t stream) {
+    if (T == 0) return 0;
+    KESTREL_REQUIRE(T > 0 && n > 0 && S > 0 && col0 >= 0 && col0 + n <= ld, "gate_columns_mul: bad sizes");
+    size_t total = (size_t)T * n;
+    unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == KESTREL_F32)
+        kestrel_launch(gate_columns_mul_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float *)x, g, S, (size_t)slice_stride, ld, col0, bias, n, total);
+    else if (dtype == KESTREL_BF16)
+        kestrel_launch(gate_columns_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16 *)x, g, S, (size_t)slice_stride, ld, col0, bias, n, total);
+    else
+        return kestrel_fail(-2, "gate_columns_mul: unknown dtype %d", dtype);
+    return kestrel_check_launch("gate_columns_mul");
+}
+
+// ------------------------------------------------------------------------------------------
+// x[t, :] += row[:] for every token: a learned vector fed into the stream (in front of a pass over a stretch of layers)
+// ------------------------------------------------------------------------------------------
+__global__ void add_row_kernel(float *__restrict__ x, const float *__restrict__ row, int d, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < n) x[idx] += row[idx % d];
+}
+
+KESTREL_API int kestrel_add_row(float *x, const float *row, int T, int d, cudaStream_t stream) {
+    if (T == 0) return 0;
+    KESTREL_REQUIRE(T > 0 && d > 0, "add_row: bad sizes");
+    size_t n = (size_t)T * d;
+    kestrel_launch(add_row_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, row, d, n);
+    return kestrel_check_launch("add_row");
+}
+
+// ------------------------------------------------------------------------------------------
+// out[t, :] = table[ids[t], :] * scale, float32: an embedding with a constant factor
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_scaled_kernel(const T *__restrict__ table, const int *__restrict__ ids, float *__restrict__ out, int d, float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const T *row = table + (size_t)ids[t] * d;
+    float *o = out + (size_t)t * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = to_f32<T>(row[i]) * scale;
+}
+
+KESTREL_API int kestrel_embed_scaled(const void *table, int dtype, const int *ids, float *out, int T, int d, float scale, cudaStream_t stream) {
+    if (T == 0) return 0;
+    KESTREL_REQUIRE(T > 0 && d > 0, "embed_scaled: bad sizes T=%d d=%d", T, d);
+    if (dtype == KESTREL_F32)
+        kestrel_launch(embed_scaled_kernel<float>, dim3(T), dim3(256), 0, stream, (const float *)table, ids, out, d, scale);
+    else if (dtype == KESTREL_BF16)
+        kestrel_launch(embed_scaled_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, (const __nv_bfloat16 *)table, ids, out, d, scale);
+    else
+        return kestrel_fail(-2, "embed_scaled: unknown dtype %d", dtype);
+    return kestrel_check_launch("embed_scaled");
 }

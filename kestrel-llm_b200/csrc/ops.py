@@ -151,14 +151,18 @@ class Partials:
         return out
 
 
-def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t] = table[ids[t]] widened to float32."""
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """out[t] = table[ids[t]] widened to float32, times ``scale``."""
     _need(table, "embed.table", dims=2)
     _need(ids, "embed.ids", torch.int32, 1)
     _need(out, "embed.out", torch.float32, 2)
     T, d = out.shape
     if ids.shape[0] != T or table.shape[1] != d:
         raise KernelError(f"embed: ids {tuple(ids.shape)}, table {tuple(table.shape)}, out {tuple(out.shape)}")
+    if scale != 1.0:
+        _check(library().kestrel_embed_scaled(table.data_ptr(), _code(table, "embed.table"), ids.data_ptr(), out.data_ptr(), T, d, float(scale),
+                                              _stream()))
+        return
     _check(library().kestrel_embed(table.data_ptr(), _code(table, "embed.table"), ids.data_ptr(),
                                    out.data_ptr(), T, d, _stream()))
 
@@ -758,18 +762,25 @@ def add_sinusoid(x: torch.Tensor, positions: torch.Tensor, freq: torch.Tensor) -
     _check(library().kestrel_add_sinusoid(x.data_ptr(), positions.data_ptr(), freq.data_ptr(), T, d, _stream()))
 
 
-def add_two(residual: torch.Tensor, a: Partials, b: Optional[Partials], cast: Optional[torch.Tensor]) -> None:
-    """residual += a + b (the sums of their slices, a's first); ``cast``, if given, receives the
-    new residual stream in its own dtype."""
+def add_two(residual: torch.Tensor, a: Partials, b: Optional[Partials], cast: Optional[torch.Tensor], c: Optional[Partials] = None) -> None:
+    """residual += a + b (the sums of their slices, a's first), + c where a third product is given;
+    ``cast``, if given, receives the new residual stream in its own dtype."""
     _need(residual, "add_two.residual", torch.float32, 2)
     T, d = residual.shape
-    for p in (a, b):
+    if b is None and c is not None:
+        b, c = c, None
+    for p in (a, b, c):
         if p is not None and (p.tokens != T or p.width != d or p.bias is not None):
             raise KernelError("add_two: a product does not fit the residual stream, or carries a bias")
     if cast is not None:
         _need(cast, "add_two.cast", dims=2)
         if cast.shape != residual.shape:
             raise KernelError("add_two: cast and residual differ in shape")
+    if c is not None:
+        _check(library().kestrel_add_three(residual.data_ptr(), a.data.data_ptr(), a.slices, a.slice_stride, b.data.data_ptr(), b.slices,
+                                           b.slice_stride, c.data.data_ptr(), c.slices, c.slice_stride, _p(cast),
+                                           _code(cast, "add_two.cast") if cast is not None else F32, T, d, _stream()))
+        return
     _check(library().kestrel_add_two(residual.data_ptr(), a.data.data_ptr(), a.slices, a.slice_stride,
                                      _p(b.data) if b is not None else None, b.slices if b is not None else 0,
                                      b.slice_stride if b is not None else 0, _p(cast),
@@ -809,12 +820,12 @@ def partial_columns(p: Partials, col0: int, n: int, dtype: torch.dtype) -> torch
     return out
 
 
-COLUMN_ACTS = {None: 0, "none": 0, "relu2": 1, "tanh": 2, "silu": 3}
+COLUMN_ACTS = {None: 0, "none": 0, "relu2": 1, "tanh": 2, "silu": 3, "gelu": 4, "gelu_tanh": 5}
 
 
 def partial_columns_act(p: Partials, col0: int, n: int, dtype: torch.dtype, act: Optional[str]) -> torch.Tensor:
     """act(columns [col0, col0 + n) of a product, summed over its slices, plus its bias) in ``dtype``;
-    ``act`` None, "relu2" (the square of relu), "tanh" or "silu"."""
+    ``act`` None, "relu2" (the square of relu), "tanh", "silu", "gelu" (the exact one, with erf) or "gelu_tanh"."""
     if act not in COLUMN_ACTS:
         raise KernelError(f"partial_columns_act: activation {act!r} is none of {', '.join(str(k) for k in COLUMN_ACTS)}")
     out = torch.empty((p.tokens, n), dtype=dtype, device=p.data.device)
@@ -875,6 +886,26 @@ def embed_add(table: torch.Tensor, ids: torch.Tensor, x: torch.Tensor) -> None:
                                        _stream()))
 
 
+def gate_columns_mul(x: torch.Tensor, g: Partials, col0: int) -> None:
+    """x[t, i] *= sigmoid(columns [col0, col0 + x.shape[1]) of a product, summed over its slices, plus its bias), in place:
+    a gate per element of a mixer's output."""
+    _need(x, "gate_columns_mul.x", dims=2)
+    T, n = x.shape
+    if g.tokens != T or col0 < 0 or col0 + n > g.width or (g.bias is not None and g.bias.shape[0] != g.width):
+        raise KernelError("gate_columns_mul: shapes differ")
+    _check(library().kestrel_gate_columns_mul(x.data_ptr(), _code(x, "gate_columns_mul.x"), g.data.data_ptr(), g.slices, g.slice_stride, g.width,
+                                              int(col0), _p(g.bias), T, n, _stream()))
+
+
+def add_row(x: torch.Tensor, row: torch.Tensor) -> None:
+    """x[t] += row for every token: float32 [T, d] and float32 [d]."""
+    _need(x, "add_row.x", torch.float32, 2)
+    _need(row, "add_row.row", torch.float32, 1)
+    if row.shape[0] != x.shape[1]:
+        raise KernelError("add_row: the row does not fit the stream")
+    _check(library().kestrel_add_row(x.data_ptr(), row.data_ptr(), x.shape[0], x.shape[1], _stream()))
+
+
 def logit_scale_cap(logits: torch.Tensor, scale: float, cap: float) -> None:
     """In place: logits * scale, then cap * tanh(. / cap) where cap > 0."""
     _need(logits, "logit_scale_cap.logits", torch.float32, 2)
@@ -890,14 +921,15 @@ QK_NORM_MODES = {None: 0, False: 0, "none": 0, True: 1, "head": 1, "projection":
 def attn_prepare_ex(qkv: Partials, q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], qk_norm, norm_eps: float,
                     positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor, page_size: int,
                     k_cache: torch.Tensor, v_cache: torch.Tensor, q_out: torch.Tensor, gate_out: Optional[torch.Tensor],
-                    nq: int, nkv: int, hd: int, vd: int, has_kv: bool, v_norm: bool = False, rotation=None) -> None:
+                    nq: int, nkv: int, hd: int, vd: int, has_kv: bool, v_norm: bool = False, rotation=None, q_temp=None) -> None:
     """Columns [q | k | v | gate] of a fused product, plus the product's bias where it carries one:
     q and k divided by their root mean square - ``qk_norm`` "head" (or True): per head, times a
     weight [hd] where given; "projection": over all of q's columns at once and all of k's, times
     weights [nq hd] and [nkv hd]; None: left as they are - and v per head if ``v_norm``; q to
     ``q_out``, k and v into the cache pages (absent if ``has_kv`` is False), sigmoid of the gate
     columns to ``gate_out`` float32 [T, nq].  With ``rotation`` (a `Rotation` of parts/base.py: frequencies,
-    rotated size, pairing, scale) q and k are turned by position after their norm."""
+    rotated size, pairing, scale) q and k are turned by position after their norm.  ``q_temp`` = (coef, every): q
+    times 1 + coef ln(floor((position + 1) / every) + 1), a temperature that grows with the position."""
     _need(q_out, "attn_prepare_ex.q_out", dims=2)
     _need(block_table, "attn_prepare_ex.block_table", torch.int32, 2)
     _need(k_cache, "attn_prepare_ex.k_cache", q_out.dtype, 4)
@@ -926,9 +958,16 @@ def attn_prepare_ex(qkv: Partials, q_norm_w: Optional[torch.Tensor], k_norm_w: O
         _need(inv_freq, "attn_prepare_ex.inv_freq", torch.float32, 1)
         if rot <= 0 or rot % 2 or rot > hd or inv_freq.shape[0] < rot // 2:
             raise KernelError(f"attn_prepare_ex: {rot} rotated dimensions of a head of {hd} with {inv_freq.shape[0]} frequencies")
-    _check(library().kestrel_attn_prepare_rotated(
+    if mode == 1:
+        for w, name in ((q_norm_w, "q"), (k_norm_w, "k")):
+            if w is not None and (w.dtype != torch.float32 or w.numel() != hd):
+                raise KernelError(f"attn_prepare_ex: the norm per head takes a float32 weight of {hd} entries for {name}")
+    t_coef, t_every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 0)
+    if q_temp and t_every <= 0:
+        raise KernelError("attn_prepare_ex: a query temperature needs a positive number of positions a step")
+    _check(library().kestrel_attn_prepare_tempered(
         qkv.data.data_ptr(), qkv.slices, qkv.slice_stride, qkv.width, _p(qkv.bias), _p(q_norm_w), _p(k_norm_w), mode, 1 if v_norm else 0,
-        float(norm_eps), _p(inv_freq), rot or 0, rot_mode or 0, float(rotation.scale) if rotation is not None else 1.0, positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(), block_table.stride(0), int(page_size),
+        float(norm_eps), _p(inv_freq), rot or 0, rot_mode or 0, float(rotation.scale) if rotation is not None else 1.0, t_coef, t_every, positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(), block_table.stride(0), int(page_size),
         k_cache.data_ptr(), v_cache.data_ptr(), q_out.data_ptr(), _p(gate_out), _code(q_out, "attn_prepare_ex.q_out"), T, nq, nkv, hd, vd,
         1 if has_kv else 0, _stream()))
 
@@ -942,12 +981,18 @@ class ScoreOptions:
     neither): s <- s - r1[h] ln(1 + r2[h] (i - j)) for the key j behind the query i; ``weighting``
     "softmax", "softmax_sink" (one more term in the denominator, without a value: exp(sink[h]) with
     ``sink`` float32 [heads], exp(0) without it) or "sigmoid" (every visible key weighs
-    sigmoid(s + head_bias[h]), nothing is normalised)."""
+    sigmoid(s + head_bias[h]), nothing is normalised).  ``rel`` (float32 [buckets, heads]) with ``rel_bucket``
+    (int32 [far + 1], the bucket of every distance up to ``far``; longer distances share far's): s <- s +
+    rel[bucket(i - j), h], a learned number per head and bucket of distances."""
 
-    __slots__ = ("softcap", "r1", "r2", "head_bias", "weighting", "sink")
+    __slots__ = ("softcap", "r1", "r2", "head_bias", "weighting", "sink", "rel", "rel_bucket")
 
     def __init__(self, softcap: float = 0.0, r1: Optional[torch.Tensor] = None, r2: Optional[torch.Tensor] = None,
-                 head_bias: Optional[torch.Tensor] = None, weighting: str = "softmax", sink: Optional[torch.Tensor] = None):
+                 head_bias: Optional[torch.Tensor] = None, weighting: str = "softmax", sink: Optional[torch.Tensor] = None,
+                 rel: Optional[torch.Tensor] = None, rel_bucket: Optional[torch.Tensor] = None):
+        if (rel is None) != (rel_bucket is None):
+            raise KernelError("a table of distance terms needs the buckets of the distances, and the other way round")
+        self.rel, self.rel_bucket = rel, rel_bucket
         if weighting not in WEIGHTINGS:
             raise KernelError(f"weighting '{weighting}' is none of {', '.join(WEIGHTINGS)}")
         if (r1 is None) != (r2 is None):
@@ -965,6 +1010,16 @@ class ScoreOptions:
                 if t.shape[0] != nq:
                     raise KernelError(f"score.{name}: {t.shape[0]} entries for {nq} heads")
         return self.softcap, _p(self.r1), _p(self.r2), _p(self.head_bias), WEIGHTINGS[self.weighting], _p(self.sink)
+
+    def rel_args(self, nq: int):
+        """(table, buckets, longest distance with a bucket of its own) for the kernels that take the distance table."""
+        if self.rel is None:
+            return None, None, 0
+        _need(self.rel, "score.rel", torch.float32, 2)
+        _need(self.rel_bucket, "score.rel_bucket", torch.int32, 1)
+        if self.rel.shape[1] != nq or self.rel_bucket.shape[0] < 1:
+            raise KernelError(f"score.rel: {tuple(self.rel.shape)} for {nq} heads")
+        return self.rel.data_ptr(), self.rel_bucket.data_ptr(), self.rel_bucket.shape[0] - 1
 
 
 _NO_SCORE = ScoreOptions()
@@ -987,10 +1042,10 @@ def attention_plain_ex(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
         raise KernelError("attention: shapes differ")
     if gate is not None:
         _need(gate, "attention.gate", torch.float32, 2)
-    _check(library().kestrel_attention_plain_scored(
+    _check(library().kestrel_attention_plain_biased(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
         block_table.stride(0), int(page_size), out.data_ptr(), _code(q, "attention.q"), T, nq, nkv, hd, vd, int(window), int(keep_first),
-        _p(gate), float(scale), *(score or _NO_SCORE).args(nq), _stream()))
+        _p(gate), float(scale), *(score or _NO_SCORE).args(nq), *(score or _NO_SCORE).rel_args(nq), _stream()))
 
 
 def attention_window_supported(hd: int, vd: int, nq: int, nkv: int) -> bool:
@@ -1024,10 +1079,10 @@ def attention_window(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     scratch = None
     if ksplit > 1:
         scratch = torch.empty(lib.kestrel_attention_window_scratch_floats(int(batch.num_seqs), int(batch.max_count), nq, nkv, hd, vd, ksplit), dtype=torch.float32, device=q.device)
-    _check(lib.kestrel_attention_window_scored(
+    _check(lib.kestrel_attention_window_biased(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _p(gate), batch.cu_seqlens.data_ptr(), batch.kv_lens.data_ptr(),
         block_table.data_ptr(), block_table.stride(0), int(page_size), int(batch.num_seqs), int(batch.max_count), nq, nkv, hd, vd, int(window),
-        int(keep_first), float(scale), *(score or _NO_SCORE).args(nq), ksplit, _p(scratch), _stream()))
+        int(keep_first), float(scale), *(score or _NO_SCORE).args(nq), *(score or _NO_SCORE).rel_args(nq), ksplit, _p(scratch), _stream()))
     if ksplit > 1:
         global launches
         launches += 1          # the merge kernel
@@ -1063,20 +1118,29 @@ def row_tiles(batch, rows_per_token: int, rows_per_tile: int = 256):
 
 def latent_prepare(fused: Partials, q_norm_w: torch.Tensor, kv_norm_w: torch.Tensor, norm_eps: float, positions: torch.Tensor,
                    seq_of_token: torch.Tensor, block_table: torch.Tensor, page_size: int, latent_cache: torch.Tensor, q_out: torch.Tensor,
-                   gate_out: Optional[torch.Tensor], kv_out: Optional[torch.Tensor] = None) -> None:
-    """Columns [query latent | key/value latent | gate] of a fused product: both latents RMS-normed
+                   gate_out: Optional[torch.Tensor], kv_out: Optional[torch.Tensor] = None, rot_cols: int = 0, rotation=None) -> None:
+    """Columns [query latent | key/value latent | shared key part | gate] of a fused product: both latents RMS-normed
     with their weights; the query latent to ``q_out`` [T, q_rank], the key/value latent into the
     token's slot of ``latent_cache`` [pages, 1, page size, kv_rank], sigmoid of the gate columns to
     ``gate_out`` float32 [T, heads]; ``kv_out`` [T, kv_rank], if given, receives the step's key/value
-    latents as rows too."""
+    latents as rows too.  With ``rot_cols`` the cache rows are [latent | ``rot_cols`` more]: a key part that all heads
+    share, not normed, turned by position as ``rotation`` (a `Rotation` of parts/base.py) says."""
     _need(q_out, "latent_prepare.q_out", dims=2)
     _need(latent_cache, "latent_prepare.latent_cache", q_out.dtype, 4)
     _need(q_norm_w, "latent_prepare.q_norm_w", torch.float32, 1)
     _need(kv_norm_w, "latent_prepare.kv_norm_w", torch.float32, 1)
     _need(block_table, "latent_prepare.block_table", torch.int32, 2)
     T, q_rank = q_out.shape
-    kv_rank = latent_cache.shape[3]
+    kv_rank = latent_cache.shape[3] - int(rot_cols)
     n_gate = 0
+    inv_freq, rot, rot_mode, rot_scale = None, 0, 0, 1.0
+    if rotation is not None:
+        inv_freq, rot, rot_mode, rot_scale = rotation.inv_freq, int(rotation.dim), rotation.mode, float(rotation.scale)
+        _need(inv_freq, "latent_prepare.inv_freq", torch.float32, 1)
+        if rot > rot_cols or rot % 2 or inv_freq.shape[0] < rot // 2:
+            raise KernelError(f"latent_prepare: {rot} rotated dimensions of a key part of {rot_cols}")
+    if kv_rank <= 0 or rot_cols < 0:
+        raise KernelError("latent_prepare: the cache rows are shorter than the shared key part")
     if gate_out is not None:
         _need(gate_out, "latent_prepare.gate_out", torch.float32, 2)
         n_gate = gate_out.shape[1]
@@ -1087,10 +1151,28 @@ def latent_prepare(fused: Partials, q_norm_w: torch.Tensor, kv_norm_w: torch.Ten
     if fused.tokens != T or fused.bias is not None or latent_cache.shape[1] != 1 or latent_cache.shape[2] != page_size or \
             q_norm_w.shape[0] != q_rank or kv_norm_w.shape[0] != kv_rank or (gate_out is not None and gate_out.shape[0] != T):
         raise KernelError("latent_prepare: shapes differ, or a bias is pending")
-    _check(library().kestrel_latent_prepare(
+    _check(library().kestrel_latent_prepare_rotated(
         fused.data.data_ptr(), fused.slices, fused.slice_stride, fused.width, q_norm_w.data_ptr(), kv_norm_w.data_ptr(), float(norm_eps),
         positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(), block_table.stride(0), int(page_size), latent_cache.data_ptr(),
-        q_out.data_ptr(), _p(gate_out), _p(kv_out), _code(q_out, "latent_prepare.q_out"), T, q_rank, kv_rank, n_gate, _stream()))
+        q_out.data_ptr(), _p(gate_out), _p(kv_out), _code(q_out, "latent_prepare.q_out"), T, q_rank, kv_rank, n_gate, int(rot_cols), _p(inv_freq),
+        rot, rot_mode, rot_scale, _stream()))
+
+
+def latent_rotate_queries(q: torch.Tensor, heads: int, d: int, rot_cols: int, q_lat: torch.Tensor, col0: int, positions: torch.Tensor,
+                          rotation) -> None:
+    """Columns [d, d + rot_cols) of every head of q [T, heads * (d + rot_cols)], turned by position as ``rotation`` says (None:
+    copied), into columns [col0, col0 + rot_cols) of every head of q_lat [T, heads * (col0 + rot_cols)]."""
+    _need(q, "latent_rotate_queries.q", dims=2)
+    _need(q_lat, "latent_rotate_queries.q_lat", q.dtype, 2)
+    T = q.shape[0]
+    if q.shape[1] != heads * (d + rot_cols) or q_lat.shape != (T, heads * (col0 + rot_cols)):
+        raise KernelError("latent_rotate_queries: shapes differ")
+    inv_freq, rot, rot_mode, rot_scale = None, 0, 0, 1.0
+    if rotation is not None:
+        inv_freq, rot, rot_mode, rot_scale = rotation.inv_freq, int(rotation.dim), rotation.mode, float(rotation.scale)
+    _check(library().kestrel_latent_rotate_queries(q.data_ptr(), q.stride(0), d + rot_cols, d, q_lat.data_ptr(), q_lat.stride(0), col0 + rot_cols, col0,
+                                                   positions.data_ptr(), _code(q, "latent_rotate_queries.q"), T, heads, rot_cols, _p(inv_freq), rot,
+                                                   rot_mode, rot_scale, _stream()))
 
 
 def head_scale(x: torch.Tensor, gate: torch.Tensor, heads: int) -> None:
@@ -1103,26 +1185,32 @@ def head_scale(x: torch.Tensor, gate: torch.Tensor, heads: int) -> None:
     _check(library().kestrel_head_scale(x.data_ptr(), gate.data_ptr(), _code(x, "head_scale.x"), T, heads, x.shape[1] // heads, _stream()))
 
 
-def head_gemm(x: torch.Tensor, w: torch.Tensor, heads: int, w_kn: bool, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def head_gemm(x: torch.Tensor, w: torch.Tensor, heads: int, w_kn: bool, out: Optional[torch.Tensor] = None,
+              x_head_stride: Optional[int] = None, out_head_stride: Optional[int] = None, out_f32: bool = False) -> torch.Tensor:
     """Every head's columns of x [T, heads * K] times that head's own matrix, a slice of ``w``:
     ``w_kn`` False: w [heads * N, K], out_h = x_h w_h^T; True: w [heads * K, N], out_h = x_h w_h (the
-    transposed use of an expansion).  Returns [T, heads * N] in x's dtype; float32 sums."""
+    transposed use of an expansion).  Returns [T, heads * N] in x's dtype (float32 if ``out_f32``); float32 sums.
+    ``x_head_stride`` / ``out_head_stride``: a head's K input columns start every so many columns of x, its N
+    output columns every so many columns of ``out`` (heads whose columns lie among others)."""
     _need(x, "head_gemm.x", dims=2)
     _need(w, "head_gemm.w", x.dtype, 2)
     T = x.shape[0]
-    if x.shape[1] % heads or w.shape[0] % heads:
+    hsx = x.shape[1] // heads if x_head_stride is None else int(x_head_stride)
+    if (x_head_stride is None and x.shape[1] % heads) or w.shape[0] % heads:
         raise KernelError("head_gemm: the columns of x or the rows of w do not divide by the heads")
-    K = x.shape[1] // heads
+    K = w.shape[0] // heads if w_kn else w.shape[1]
     N = w.shape[1] if w_kn else w.shape[0] // heads
-    if (w_kn and w.shape[0] != heads * K) or (not w_kn and w.shape[1] != K):
+    hso = N if out_head_stride is None else int(out_head_stride)
+    if K > hsx or N > hso or x.shape[1] < (heads - 1) * hsx + K:
         raise KernelError(f"head_gemm: x {tuple(x.shape)}, w {tuple(w.shape)}, {heads} heads")
+    out_dtype = torch.float32 if out_f32 else x.dtype
     if out is None:
-        out = torch.empty((T, heads * N), dtype=x.dtype, device=x.device)
-    _need(out, "head_gemm.out", x.dtype, 2)
-    if out.shape != (T, heads * N):
+        out = torch.empty((T, heads * hso), dtype=out_dtype, device=x.device)
+    _need(out, "head_gemm.out", out_dtype, 2)
+    if out.shape[0] != T or out.shape[1] < (heads - 1) * hso + N:
         raise KernelError("head_gemm: out has the wrong shape")
-    _check(library().kestrel_head_gemm(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), 1 if w_kn else 0, out.data_ptr(), out.stride(0),
-                                       _code(x, "head_gemm.x"), T, heads, N, K, _stream()))
+    _check(library().kestrel_head_gemm_strided(x.data_ptr(), x.stride(0), hsx, w.data_ptr(), w.stride(0), 1 if w_kn else 0, out.data_ptr(),
+                                               out.stride(0), hso, 1 if out_f32 else 0, _code(x, "head_gemm.x"), T, heads, N, K, _stream()))
     return out
 
 
@@ -1290,6 +1378,114 @@ def moe_route(z: Partials, bias: Optional[torch.Tensor], top: int):
     _check(library().kestrel_moe_route(z.data.data_ptr(), z.slices, z.slice_stride, _p(bias), ids.data_ptr(), w.data_ptr(), T, E, top,
                                        _stream()))
     return ids, w
+
+
+def moe_route_sigmoid(z: Partials, correction: Optional[torch.Tensor], top: int, groups: int = 1, keep: int = 1, scale: float = 1.0):
+    """(expert ids int32 [T, top], weights float32 [T, top]) of a router with sigmoid scores: experts are chosen by
+    score + ``correction`` among the ``keep`` best of ``groups`` equal groups of neighbours (a group's score: the sum of its two
+    largest choice scores), and weighted by their scores over the chosen scores' sum, times ``scale``."""
+    T, E = z.tokens, z.width
+    if z.bias is not None:
+        raise KernelError("moe_route_sigmoid: a bias is pending")
+    if correction is not None:
+        _need(correction, "moe_route_sigmoid.correction", torch.float32, 1)
+        if correction.shape[0] != E:
+            raise KernelError("moe_route_sigmoid: a correction per expert")
+    ids = torch.empty((T, top), dtype=torch.int32, device=z.data.device)
+    w = torch.empty((T, top), dtype=torch.float32, device=z.data.device)
+    _check(library().kestrel_moe_route_sigmoid(z.data.data_ptr(), z.slices, z.slice_stride, _p(correction), int(groups), int(keep), float(scale),
+                                               ids.data_ptr(), w.data_ptr(), T, E, top, _stream()))
+    return ids, w
+
+
+UP_ACTS = {"gelu": 1, "gelu_tanh": 2, "silu": 3, "relu2": 4}
+
+
+def moe_experts_ungated(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
+                        act: str) -> torch.Tensor:
+    """The chosen experts' outputs W_down[e] act(W_up[e] x), weighted and summed per token: float32 [T, width].
+    w_up [E, ff, width], w_down [E, width, ff]; ``act`` one of `UP_ACTS`.  The pairs' input rows are gathered in the
+    order of their experts, then two grouped products run (tcgen05 from `MOE_TC_MIN_PAIRS` pairs on)."""
+    _need(x, "moe.x", dims=2)
+    _need(w_up, "moe.w_up", x.dtype, 3)
+    _need(w_down, "moe.w_down", x.dtype, 3)
+    if act not in UP_ACTS:
+        raise KernelError(f"moe_experts_ungated: activation {act!r} is none of {', '.join(UP_ACTS)}")
+    T, K = x.shape
+    E, ff, _ = w_up.shape
+    top, N = ids.shape[1], w_down.shape[1]
+    if w_up.shape[2] != K or w_down.shape != (E, N, ff) or ids.shape[0] != T:
+        raise KernelError("moe_experts_ungated: shapes differ")
+    lib, dev, P, code = library(), x.device, T * top, _code(x, "moe.x")
+    xs = torch.empty((P, K), dtype=x.dtype, device=dev)
+    a = torch.empty((P, ff), dtype=x.dtype, device=dev)
+    y = torch.empty((P, N), dtype=torch.float32, device=dev)
+    out = torch.empty((T, N), dtype=torch.float32, device=dev)
+    tc = bool(_moe_tc and x.dtype == torch.bfloat16 and P >= MOE_TC_MIN_PAIRS and
+              lib.kestrel_moe_tc_supported(xs.data_ptr(), a.data_ptr(), w_up.data_ptr(), w_down.data_ptr(), ff, K))
+    rows = lib.kestrel_moe_tc_tile_rows() if tc else MOE_TILE_ROWS
+    max_tiles = lib.kestrel_moe_max_tiles(P, E, rows)
+    meta = torch.empty((E + 1) + 2 * P + 2 * max_tiles + 1, dtype=torch.int32, device=dev)
+    offsets, row_pair, pair_row = meta[:E + 1], meta[E + 1:E + 1 + P], meta[E + 1 + P:E + 1 + 2 * P]
+    o = E + 1 + 2 * P
+    tile_expert, tile_row0, n_tiles = meta[o:o + max_tiles], meta[o + max_tiles:o + 2 * max_tiles], meta[o + 2 * max_tiles:]
+    _check(lib.kestrel_moe_group(ids.data_ptr(), P, E, rows, offsets.data_ptr(), row_pair.data_ptr(), pair_row.data_ptr(),
+                                 tile_expert.data_ptr(), tile_row0.data_ptr(), n_tiles.data_ptr(), _stream()))
+    _check(lib.kestrel_moe_gather_rows_any(x.data_ptr(), x.stride(0), row_pair.data_ptr(), top, xs.data_ptr(), code, P, K, _stream()))
+    if tc:
+        _check(lib.kestrel_moe_up_act_tc(xs.data_ptr(), w_up.data_ptr(), offsets.data_ptr(), tile_expert.data_ptr(), tile_row0.data_ptr(),
+                                         n_tiles.data_ptr(), max_tiles, UP_ACTS[act], a.data_ptr(), P, E, ff, K, _stream()))
+        _check(lib.kestrel_moe_down_tc(a.data_ptr(), w_down.data_ptr(), offsets.data_ptr(), row_pair.data_ptr(), tile_expert.data_ptr(),
+                                       tile_row0.data_ptr(), n_tiles.data_ptr(), max_tiles, weights.data_ptr(), y.data_ptr(), P, E, N, ff, _stream()))
+    else:
+        _check(lib.kestrel_moe_up_act(xs.data_ptr(), w_up.data_ptr(), offsets.data_ptr(), row_pair.data_ptr(), tile_expert.data_ptr(),
+                                      tile_row0.data_ptr(), n_tiles.data_ptr(), max_tiles, UP_ACTS[act], a.data_ptr(), code, ff, K, _stream()))
+        _check(lib.kestrel_moe_down(a.data_ptr(), w_down.data_ptr(), offsets.data_ptr(), row_pair.data_ptr(), tile_expert.data_ptr(),
+                                    tile_row0.data_ptr(), n_tiles.data_ptr(), max_tiles, weights.data_ptr(), y.data_ptr(), code, N, ff, _stream()))
+    _check(lib.kestrel_moe_combine(y.data_ptr(), pair_row.data_ptr(), top, out.data_ptr(), T, N, _stream()))
+    return out
+
+
+# ---- a diagonal recurrence with gates from its own input -------------------------------------------
+def rglru_branches(fused: Partials, conv_w: torch.Tensor, conv_b: Optional[torch.Tensor], state: torch.Tensor, tail_off: int, batch,
+                   y_out: torch.Tensor, u_out: torch.Tensor, u_st: torch.Tensor) -> None:
+    """Columns [y | x] of a fused product (plus its bias): y_out = gelu_tanh(y), u_out = causal convolution over time of x per
+    channel (``conv_w`` [C, taps], last column the current token's; ``conv_b`` [C]) as float32, ``u_st`` the same in the storage
+    type; inputs before the step come from, and the last taps - 1 inputs go to, each request's state slot at ``tail_off``."""
+    _need(conv_w, "rglru.conv_w", torch.float32, 2)
+    _need(state, "rglru.state", torch.float32, 2)
+    _need(y_out, "rglru.y_out", torch.float32, 2)
+    _need(u_out, "rglru.u_out", torch.float32, 2)
+    _need(u_st, "rglru.u_st", dims=2)
+    C, taps = conv_w.shape
+    T = y_out.shape[0]
+    if fused.tokens != T or fused.width < 2 * C or y_out.shape != (T, C) or u_out.shape != (T, C) or u_st.shape != (T, C) or \
+            (fused.bias is not None and fused.bias.shape[0] != fused.width) or (conv_b is not None and conv_b.shape[0] != C):
+        raise KernelError("rglru_branches: shapes differ")
+    _check(library().kestrel_rglru_branches(fused.data.data_ptr(), fused.slices, fused.slice_stride, fused.width, _p(fused.bias), conv_w.data_ptr(),
+                                            _p(conv_b), taps, state.data_ptr(), state.stride(0), int(tail_off), batch.seq_of_token.data_ptr(),
+                                            batch.cu_seqlens.data_ptr(), batch.slots.data_ptr(), y_out.data_ptr(), u_out.data_ptr(), u_st.data_ptr(),
+                                            _code(u_st, "rglru.u_st"), T, batch.num_seqs, C, _stream()))
+    global launches
+    launches += 1 if taps > 1 else 0
+
+
+def rglru_scan(y: torch.Tensor, u: torch.Tensor, gr: torch.Tensor, gi: torch.Tensor, r_bias: Optional[torch.Tensor],
+               i_bias: Optional[torch.Tensor], lam: torch.Tensor, rate: float, state: torch.Tensor, batch, out: torch.Tensor) -> None:
+    """Per channel: r = sigmoid(gr + r_bias), i = sigmoid(gi + i_bias), a = exp(-rate r softplus(lam)),
+    S <- a S + sqrt(1 - a^2) i u, out = S y; S float32 at the start of each request's state slot."""
+    T, C = y.shape
+    for t, name in ((y, "y"), (u, "u"), (gr, "gr"), (gi, "gi")):
+        _need(t, f"rglru_scan.{name}", torch.float32, 2)
+        if t.shape != (T, C):
+            raise KernelError("rglru_scan: shapes differ")
+    _need(lam, "rglru_scan.lam", torch.float32, 1)
+    _need(out, "rglru_scan.out", dims=2)
+    if out.shape != (T, C) or lam.shape[0] != C:
+        raise KernelError("rglru_scan: shapes differ")
+    _check(library().kestrel_rglru_scan(y.data_ptr(), u.data_ptr(), gr.data_ptr(), gi.data_ptr(), _p(r_bias), _p(i_bias), lam.data_ptr(), float(rate),
+                                        state.data_ptr(), state.stride(0), batch.cu_seqlens.data_ptr(), batch.slots.data_ptr(), out.data_ptr(),
+                                        _code(out, "rglru_scan.out"), batch.num_seqs, C, _stream()))
 
 
 def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,

@@ -164,8 +164,16 @@ KESTREL_API int kestrel_gelu_table_mul(const float *g, int S, long long slice_st
 KESTREL_API int kestrel_add_normed(float *residual, const float *p, int S, long long slice_stride, const float *w, float eps, int T, int d, kestrel_stream_t stream);
 /* out[t, i] = sum of p's slices at [t, col0 + i], i < n, in the storage type */
 KESTREL_API int kestrel_partial_columns(const float *p, int S, long long slice_stride, int ld, int col0, void *out, int dtype, int T, int n, kestrel_stream_t stream);
-/* the same with the product's bias (NULL: none; indexed like the product's columns) and an activation on the sum: 0 none, 1 relu squared, 2 tanh, 3 silu */
+/* the same with the product's bias (NULL: none; indexed like the product's columns) and an activation on the sum: 0 none, 1 relu squared, 2 tanh, 3 silu, 4 gelu (erf), 5 gelu (tanh form) */
 KESTREL_API int kestrel_partial_columns_act(const float *p, int S, long long slice_stride, int ld, int col0, const float *bias, int act, void *out, int dtype, int T, int n, kestrel_stream_t stream);
+/* residual += sum of a's + b's + c's slices (b, c may be NULL), (a + b) + c; cast = residual in the storage type (may be NULL) */
+KESTREL_API int kestrel_add_three(float *residual, const float *a, int Sa, long long stride_a, const float *b, int Sb, long long stride_b, const float *c, int Sc, long long stride_c, void *cast, int cast_dtype, int T, int d, kestrel_stream_t stream);
+/* x[t, i] *= sigmoid(sum of g's slices at [t, col0 + i] + bias[col0 + i]), i < n, in place in the storage type (bias may be NULL) */
+KESTREL_API int kestrel_gate_columns_mul(void *x, int dtype, const float *g, int S, long long slice_stride, int ld, int col0, const float *bias, int T, int n, kestrel_stream_t stream);
+/* x[t, :] += row[:] */
+KESTREL_API int kestrel_add_row(float *x, const float *row, int T, int d, kestrel_stream_t stream);
+/* out[t, :] = table[ids[t], :] * scale, float32 */
+KESTREL_API int kestrel_embed_scaled(const void *table, int dtype, const int *ids, float *out, int T, int d, float scale, kestrel_stream_t stream);
 /* out[t] = mix (a / sqrt(mean(a^2) + eps) wa + b / sqrt(mean(b^2) + eps) wb), a and b the sums of two products' slices, float32 */
 KESTREL_API int kestrel_combine_normed(const float *a, int Sa, long long stride_a, const float *wa, const float *b, int Sb, long long stride_b, const float *wb, float eps, float mix, float *out, int T, int d, kestrel_stream_t stream);
 /* v = (sum of y's slices + y_bias) * sigmoid(sum of g's slices + g_bias) (g may be NULL: no gate); residual[t] += v / sqrt(mean(v^2) + eps) w; with next_w also next_out[t] = residual[t] / sqrt(mean(residual[t]^2) + eps_next) next_w in the storage type */
@@ -189,7 +197,10 @@ KESTREL_API int kestrel_attention_window(const void *q, const void *k_cache, con
    weighting 0: softmax; 1: softmax with a valueless extra term exp(sink[h]) in the denominator (sink [nq], or NULL for
    exp(0)); 2: every visible key weighs sigmoid(s + head_bias[h]) (head_bias [nq] or NULL), not normalised over keys */
 KESTREL_API int kestrel_attention_plain_scored(const void *q, const void *k_cache, const void *v_cache, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *out, int dtype, int T, int nq, int nkv, int hd, int vd, int window, int keep_first, const float *gate, float scale, float softcap, const float *r1, const float *r2, const float *head_bias, int weighting, const float *sink, kestrel_stream_t stream);
+/* the same with rel[bucket[min(i - j, rel_far)], head] added to the scores: rel float32 [buckets, nq], rel_bucket int32 [rel_far + 1] (rel may be NULL) */
+KESTREL_API int kestrel_attention_plain_biased(const void *q, const void *k_cache, const void *v_cache, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *out, int dtype, int T, int nq, int nkv, int hd, int vd, int window, int keep_first, const float *gate, float scale, float softcap, const float *r1, const float *r2, const float *head_bias, int weighting, const float *sink, const float *rel, const int *rel_bucket, int rel_far, kestrel_stream_t stream);
 KESTREL_API int kestrel_attention_window_scored(const void *q, const void *k_cache, const void *v_cache, void *out, const float *gate, const int *cu_seqlens, const int *kv_lens, const int *block_table, int table_stride, int page_size, int nseq, int max_count, int nq, int nkv, int hd, int vd, int window, int keep_first, float scale, float softcap, const float *r1, const float *r2, const float *head_bias, int weighting, const float *sink, int ksplit, float *scratch, kestrel_stream_t stream);
+KESTREL_API int kestrel_attention_window_biased(const void *q, const void *k_cache, const void *v_cache, void *out, const float *gate, const int *cu_seqlens, const int *kv_lens, const int *block_table, int table_stride, int page_size, int nseq, int max_count, int nq, int nkv, int hd, int vd, int window, int keep_first, float scale, float softcap, const float *r1, const float *r2, const float *head_bias, int weighting, const float *sink, const float *rel, const int *rel_bucket, int rel_far, int ksplit, float *scratch, kestrel_stream_t stream);
 /* a step of single tokens may cut its key rounds into `ksplit` shares, a CTA each, merged by a second kernel; scratch of kestrel_attention_window_scratch_floats floats */
 KESTREL_API int kestrel_attention_window_splits(int nseq, int max_count, int nq, int nkv, int hd, int vd, int window, int max_kv_len);
 KESTREL_API long long kestrel_attention_window_scratch_floats(int nseq, int max_count, int nq, int nkv, int hd, int vd, int ksplit);
@@ -198,14 +209,22 @@ KESTREL_API int kestrel_attention_tc_scored(const void *q, const void *k_cache, 
 KESTREL_API int kestrel_attn_prepare_normed(const float *partial, int S, long long slice_stride, int ld, const float *bias, const float *q_norm_w, const float *k_norm_w, int qk_norm, int v_norm, float norm_eps, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *k_cache, void *v_cache, void *q_out, float *gate_out, int dtype, int T, int nq, int nkv, int hd, int vd, int has_kv, kestrel_stream_t stream);
 /* attn_prepare_normed, then q and k turned by position where inv_freq is given: pair j of a head's first `rot` dimensions by position * inv_freq[j]; rot_mode 0 pairs j with j + rot / 2, 1 pairs 2j with 2j + 1; rot_scale multiplies cos and sin */
 KESTREL_API int kestrel_attn_prepare_rotated(const float *partial, int S, long long slice_stride, int ld, const float *bias, const float *q_norm_w, const float *k_norm_w, int qk_norm, int v_norm, float norm_eps, const float *inv_freq, int rot, int rot_mode, float rot_scale, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *k_cache, void *v_cache, void *q_out, float *gate_out, int dtype, int T, int nq, int nkv, int hd, int vd, int has_kv, kestrel_stream_t stream);
+/* the same with a query temperature: q times 1 + q_temp_coef ln(floor((position + 1) / q_temp_every) + 1); q_temp_every = 0: none */
+KESTREL_API int kestrel_attn_prepare_tempered(const float *partial, int S, long long slice_stride, int ld, const float *bias, const float *q_norm_w, const float *k_norm_w, int qk_norm, int v_norm, float norm_eps, const float *inv_freq, int rot, int rot_mode, float rot_scale, float q_temp_coef, int q_temp_every, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *k_cache, void *v_cache, void *q_out, float *gate_out, int dtype, int T, int nq, int nkv, int hd, int vd, int has_kv, kestrel_stream_t stream);
 
 /* ---- attention over cached latents (attention_latent.cu) ---- */
 /* product columns [q latent: q_rank | kv latent: kv_rank | gate: n_gate]: both latents RMS-normed with their weights; the query latent to q_out [T, q_rank], the kv latent into the token's slot of latent_cache [pages, 1, page_size, kv_rank], sigmoid of the gate columns to gate_out [T, n_gate]; kv_out (may be NULL) receives the kv latents as rows [T, kv_rank] too */
 KESTREL_API int kestrel_latent_prepare(const float *partial, int S, long long slice_stride, int ld, const float *q_norm_w, const float *kv_norm_w, float norm_eps, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *latent_cache, void *q_out, float *gate_out, void *kv_out, int dtype, int T, int q_rank, int kv_rank, int n_gate, kestrel_stream_t stream);
+/* the same with rot_cols more columns between the kv latent and the gates: a key part shared by all heads, not normed, its first `rot` dimensions turned by position (rot_mode 0 halves, 1 neighbours; rot_scale on cos and sin); a cache row is [latent | key part] */
+KESTREL_API int kestrel_latent_prepare_rotated(const float *partial, int S, long long slice_stride, int ld, const float *q_norm_w, const float *kv_norm_w, float norm_eps, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *latent_cache, void *q_out, float *gate_out, void *kv_out, int dtype, int T, int q_rank, int kv_rank, int n_gate, int rot_cols, const float *inv_freq, int rot, int rot_mode, float rot_scale, kestrel_stream_t stream);
+/* q_lat[t, h out_head_stride + col0 + i] = column d + i of head h of q (head_stride columns a head), i < rot_cols, the first `rot` turned by position */
+KESTREL_API int kestrel_latent_rotate_queries(const void *q, int ldq, int head_stride, int d, void *q_lat, int ldo, int out_head_stride, int col0, const int *positions, int dtype, int T, int H, int rot_cols, const float *inv_freq, int rot, int rot_mode, float rot_scale, kestrel_stream_t stream);
 /* x[t, h, :] *= gate[t, h] in place, x [T, heads d] in the storage type */
 KESTREL_API int kestrel_head_scale(void *x, const float *gate, int dtype, int T, int heads, int d, kestrel_stream_t stream);
 /* out[t, h N + n] = sum_k x[t, h K + k] w_h[n, k]; w_kn = 0: w_h = rows [h N, (h + 1) N) of w [H N, K]; w_kn = 1: w_h[n, k] = w[h K + k, n] of w [H K, N]; all in the storage type, float32 sums */
 KESTREL_API int kestrel_head_gemm(const void *x, int ldx, const void *w, int ldw, int w_kn, void *out, int ldo, int dtype, int T, int H, int N, int K, kestrel_stream_t stream);
+/* the same with head h's input at x[t, h hsx + k] and its output at out[t, h hso + n], float32 output if out_f32 */
+KESTREL_API int kestrel_head_gemm_strided(const void *x, int ldx, int hsx, const void *w, int ldw, int w_kn, void *out, int ldo, int hso, int out_f32, int dtype, int T, int H, int N, int K, kestrel_stream_t stream);
 KESTREL_API void kestrel_head_gemm_set_plain(int on);   /* 1: bfloat16 head-wise products take the CUDA-core kernel too; for tests of both */
 
 /* ---- gated delta rule with a decay per key channel (delta_rule.cu); state slot = [S: H d dv | tail: (taps - 1) C] float32 ---- */
@@ -213,6 +232,10 @@ KESTREL_API int kestrel_delta_conv_silu(const float *partial, int S, long long s
 KESTREL_API int kestrel_delta_gates(const float *act, int C, const float *partial, int S, long long slice_stride, int ld, int col_beta, const float *a_part, int Sa, long long a_stride, const float *A_log, const float *dt_bias, float *qn, float *kn, float *decay, float *beta, int T, int H, int G, int d, kestrel_stream_t stream);
 KESTREL_API int kestrel_delta_scan(const float *qn, const float *kn, const float *decay, const float *act, int C, int col_v, const float *beta, float *state, long long state_stride, const int *cu_seqlens, const int *slots, float *out, int nseq, int H, int G, int d, int dv, kestrel_stream_t stream);
 KESTREL_API int kestrel_delta_out(const float *o, const float *w, float eps, const float *g_part, int Sg, long long g_stride, void *out, int dtype, int T, int H, int dv, kestrel_stream_t stream);
+
+/* ---- a diagonal recurrence with gates made from its own input (rglru.cu); state slot = [S: C | tail: (taps - 1) C] float32 ---- */
+KESTREL_API int kestrel_rglru_branches(const float *partial, int S, long long slice_stride, int ld, const float *bias, const float *conv_w, const float *conv_b, int taps, float *state, long long state_stride, long long tail_off, const int *seq_of_token, const int *cu_seqlens, const int *slots, float *y_out, float *u_out, void *u_st, int dtype, int T, int nseq, int C, kestrel_stream_t stream);
+KESTREL_API int kestrel_rglru_scan(const float *y, const float *u, const float *gr, const float *gi, const float *r_bias, const float *i_bias, const float *lam, float rate, float *state, long long state_stride, const int *cu_seqlens, const int *slots, void *out, int dtype, int nseq, int C, kestrel_stream_t stream);
 
 /* ---- linear recurrences S_t = diag(w) S + a (b^T S) + k v^T, o = S^T r per head (linear_recurrence.cu); S [H, d, dv] float32 at state_off of the request's state slot ---- */
 /* product columns q, f [n = H d] and v [nv = H dv]: r = silu(q), w = lower + (1 - lower) sigmoid(f + f_bias), k = 1 - w, v as it is; all float32 [T, .] */
@@ -226,17 +249,23 @@ KESTREL_API int kestrel_head_norm_gate(const float *o, const float *w, int w_str
 
 /* ---- routed feed-forward (moe.cu) ---- */
 KESTREL_API int kestrel_moe_route(const float *z_part, int S, long long slice_stride, const float *bias, int *ids, float *weights, int T, int E, int top, kestrel_stream_t stream);
+/* scores sigmoid(z); chosen by score + correction[e] (may be NULL) among the experts of the `keep` best of `n_groups` groups of neighbours (a group's score: the sum of its two largest choice scores); weights = chosen scores / (their sum + 1e-20) * scale */
+KESTREL_API int kestrel_moe_route_sigmoid(const float *z_part, int S, long long slice_stride, const float *correction, int n_groups, int keep, float scale, int *ids, float *weights, int T, int E, int top, kestrel_stream_t stream);
 KESTREL_API int kestrel_moe_max_tiles(int P, int E, int rows_per_tile);
 KESTREL_API void kestrel_moe_set_plain(int on);   /* 1: the bfloat16 grouped products take the CUDA-core kernel instead of the tensor-core one; for tests of both */
 KESTREL_API int kestrel_moe_group(const int *ids, int P, int E, int rows_per_tile, int *offsets, int *row_pair, int *pair_row, int *tile_expert, int *tile_row0, int *n_tiles, kestrel_stream_t stream);
 KESTREL_API int kestrel_moe_gate_up(const void *x, long long ldx, const void *w, const int *offsets, const int *row_pair, const int *tile_expert, const int *tile_row0, const int *n_tiles, int max_tiles, int top, float limit, void *act, int dtype, int ff, int K, kestrel_stream_t stream);
 KESTREL_API int kestrel_moe_down(const void *act, const void *w, const int *offsets, const int *row_pair, const int *tile_expert, const int *tile_row0, const int *n_tiles, int max_tiles, const float *pair_weight, float *y, int dtype, int N, int ff, kestrel_stream_t stream);
+/* experts without a gate: act [P, ff] = activation(W_up[e] xs), xs [P, K] the pairs' input rows in sorted order, w [E, ff, K]; act_kind 1 gelu (erf), 2 gelu (tanh form), 3 silu, 4 relu squared */
+KESTREL_API int kestrel_moe_up_act(const void *xs, const void *w, const int *offsets, const int *row_pair, const int *tile_expert, const int *tile_row0, const int *n_tiles, int max_tiles, int act_kind, void *act, int dtype, int ff, int K, kestrel_stream_t stream);
+KESTREL_API int kestrel_moe_gather_rows_any(const void *x, long long ldx, const int *row_pair, int top, void *xs, int dtype, int P, int K, kestrel_stream_t stream);
 /* the grouped products of many tokens on tcgen05 (moe_tcgen05.cu): tiles of kestrel_moe_tc_tile_rows() rows; xs = the pairs' input rows gathered in sorted order */
 KESTREL_API int kestrel_moe_tc_tile_rows(void);
 KESTREL_API int kestrel_moe_tc_supported(const void *xs, const void *act, const void *w_gate_up, const void *w_down, int ff, int K);
 KESTREL_API int kestrel_moe_gather_rows(const void *x, long long ldx, const int *row_pair, int top, void *xs, int P, int K, kestrel_stream_t stream);
 KESTREL_API int kestrel_moe_gate_up_tc(const void *xs, const void *w, const int *offsets, const int *tile_expert, const int *tile_row0, const int *n_tiles, int max_tiles, float limit, void *act, int P, int E, int ff, int K, kestrel_stream_t stream);
 KESTREL_API int kestrel_moe_down_tc(const void *act, const void *w, const int *offsets, const int *row_pair, const int *tile_expert, const int *tile_row0, const int *n_tiles, int max_tiles, const float *pair_weight, float *y, int P, int E, int N, int ff, kestrel_stream_t stream);
+KESTREL_API int kestrel_moe_up_act_tc(const void *xs, const void *w, const int *offsets, const int *tile_expert, const int *tile_row0, const int *n_tiles, int max_tiles, int act_kind, void *act, int P, int E, int ff, int K, kestrel_stream_t stream);
 KESTREL_API int kestrel_moe_tc_error(void);
 KESTREL_API void kestrel_moe_tc_set_ring_kb(int kb);   /* shared memory of a CTA's stages in KB: 104 (default) lets two CTAs share an SM, 200 gives one all of it; for measurements */
 KESTREL_API int kestrel_moe_combine(const float *y, const int *pair_row, int top, float *out, int T, int N, kestrel_stream_t stream);

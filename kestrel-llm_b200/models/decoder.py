@@ -6,7 +6,8 @@ uses; a block may appear in several calls (its weights run twice, each call with
 layer of its own or a shared one), and a call with ``writes_cache=False`` reads a cache layer
 that an earlier call of the same step filled; a call with ``add_embedding`` adds the embedded tokens
 to the stream once more before its block runs (a model that runs a stretch of its layers several
-times feeds them in at the start of each further pass).  The reference runs its layers in a fixed loop
+times feeds them in at the start of each further pass); a call with ``add_row`` adds a learned vector of the
+model's ``stream_rows`` to every token of the stream before its block runs.  The reference runs its layers in a fixed loop
 (src/model/vllm_safetensors.c:16404-16812); here the loop walks this list.
 """
 from __future__ import annotations
@@ -27,13 +28,15 @@ class LayerCall:
     cache: int = -1             # cache layer it uses, -1 for none
     writes_cache: bool = True   # False: attends over what an earlier call wrote
     add_embedding: bool = False  # the embedded tokens are added to the stream once more in front of this call
+    add_row: int = -1            # row of the model's `stream_rows` that is added to every token of the stream in front of this call
 
 
 class DecoderModel(Part):
     def __init__(self, config, dtype: torch.dtype, device, embedding: TokenEmbedding,
                  position: Optional[PositionEncoding], blocks: Sequence[Block],
                  order: Sequence[LayerCall], final_norm: Norm, lm_head: LMHead,
-                 optional_tensors: Sequence[str] = (), shared_parts: Sequence[Part] = (), embedding_norm: Optional[Norm] = None):
+                 optional_tensors: Sequence[str] = (), shared_parts: Sequence[Part] = (), embedding_norm: Optional[Norm] = None,
+                 stream_rows=None):
         self.config = config
         self.dtype = dtype
         self.device = torch.device(device)
@@ -46,6 +49,9 @@ class DecoderModel(Part):
         self.lm_head = lm_head
         self.optional_tensors = tuple(optional_tensors)   # may be in a checkpoint, are not used
         self.shared_parts = list(shared_parts)            # parts that several blocks use (a table all layers read): their weights are the model's
+        self.stream_rows = stream_rows                      # `StreamRows`: vectors that layer calls add to the stream, or None
+        if any(c.add_row >= 0 for c in order) and stream_rows is None:
+            raise ValueError("a layer call adds a row to the stream, but the model has no stream rows")
         n_cache = 1 + max([c.cache for c in self.order], default=-1)
         owners: List[Optional[int]] = [None] * n_cache
         for c in self.order:
@@ -93,6 +99,8 @@ class DecoderModel(Part):
             slots += self.embedding_norm.weight_slots()
         for part in self.shared_parts:
             slots += part.weight_slots()
+        if self.stream_rows is not None:
+            slots += self.stream_rows.weight_slots()
         for b in self.blocks:
             slots += b.weight_slots()
         slots += self.final_norm.weight_slots() + self.lm_head.weight_slots()
@@ -106,7 +114,7 @@ class DecoderModel(Part):
         pos_ok = (self.position is None or type(self.position).add_to_embedding is PositionEncoding.add_to_embedding) \
             and self.embedding_norm is None
         blocks_ok = all(getattr(b, "emit", None) is not None and getattr(b, "emits", False) for b in self.blocks) \
-            and not any(c.add_embedding for c in self.order) and getattr(self.lm_head, "plain", True)
+            and not any(c.add_embedding or c.add_row >= 0 for c in self.order) and getattr(self.lm_head, "plain", True)
         if not (pos_ok and blocks_ok and all(getattr(p, "emit", None) is not None
                                               for p in (self.embedding, self.final_norm, self.lm_head))):
             return None
@@ -148,6 +156,11 @@ class DecoderModel(Part):
                     ops.add_two(x, pending, None, None)
                     pending = None
                 self.embedding.add_forward(batch.token_ids, x)
+            if call.add_row >= 0:
+                if pending is not None:
+                    ops.add_two(x, pending, None, None)
+                    pending = None
+                self.stream_rows.add_forward(call.add_row, x)
             x, pending = self.blocks[call.block].forward(x, pending, batch, lc)
         return x, pending
 

@@ -20,7 +20,14 @@ denominator has one more term that carries no value: exp(0), or exp(sink[n]) wit
 per head if ``head_sink``) or "sigmoid" (every visible key weighs sigmoid(s + pb[n]), pb a number
 per head if ``head_bias``; nothing is normalised over keys).  ``position``: a `PositionEncoding` whose
 `rotary()` turns q and k (after their norm) by position - pairing, rotated size, scale and frequencies
-are its own; ``out_bias``: whether the output projection has a bias (default: as ``bias``).
+are its own; ``out_bias``: whether the output projection has a bias (default: as ``bias``).  ``head_norm_weight``:
+the norm per head multiplies by a learned weight of the head's size, one for q and one for k, shared by all heads.
+``q_temp`` = (coef, every): q times 1 + coef ln(floor((position + 1) / every) + 1).  ``distance_table`` = (rows, far):
+a learned table [rows, heads] of terms added to the scores by the bucket of the distance n = i - j - bucket(n) = n below
+rows / 2, beyond that min(rows - 1, rows / 2 + floor(ln(n / (rows / 2)) / ln(far / (rows / 2)) * (rows - rows / 2))), made
+once on the host in float64 for the distances 0 .. far.  ``element_gate``: the gate is a number per ELEMENT of the
+concatenated heads (heads * v_head_dim logits of the mixer's input, further columns of the fused product) instead of
+one per head.
 
 Kernels: float32 and head sizes that are no multiples of 8 run on the plain kernel; bfloat16 on the
 ``mma.sync`` kernel of `ops.attention_window` (single-token steps share their keys out over CTAs),
@@ -53,7 +60,8 @@ class GatedWindowAttention(Mixer):
                  names=("q", "k", "v", "g", "o"), bias: bool = False, qk_norm: Optional[str] = "head", v_norm: bool = False,
                  softcap: float = 0.0, distance_bias: bool = False, weighting: str = "softmax", head_bias: bool = False,
                  extra_names=None, position: Optional[PositionEncoding] = None, head_sink: bool = False,
-                 out_bias: Optional[bool] = None):
+                 out_bias: Optional[bool] = None, head_norm_weight: bool = False, q_temp=None, distance_table=None,
+                 element_gate: bool = False):
         if heads % kv_heads:
             raise ValueError(f"{heads} query heads are not a multiple of {kv_heads} kv heads")
         if max(head_dim, v_head_dim) > 256:
@@ -68,12 +76,16 @@ class GatedWindowAttention(Mixer):
         self.prefix, self.names, self.dtype = prefix, names, dtype
         self.q_cols = heads * head_dim
         self.kv_cols = kv_heads * (head_dim + v_head_dim) if own_kv else 0
-        self.proj = Linear(width, self.q_cols + self.kv_cols + (heads if head_gate else 0), dtype, device, bias=bias)
+        if element_gate and head_gate:
+            raise ValueError("a gate per head or a gate per element, not both")
+        self.element_gate = bool(element_gate)
+        self.gate_cols = heads if head_gate else (heads * v_head_dim if element_gate else 0)
+        self.proj = Linear(width, self.q_cols + self.kv_cols + self.gate_cols, dtype, device, bias=bias)
         self.out = Linear(heads * v_head_dim, width, dtype, device, bias=bias if out_bias is None else bool(out_bias))
         self.rotation = position.rotary() if position is not None else None
         if self.rotation is not None and self.rotation.dim > head_dim:
             raise ValueError(f"{self.rotation.dim} rotated dimensions exceed the head size {head_dim}")
-        if bias and head_gate and self.proj.bias.device.type != "meta":
+        if bias and self.gate_cols and self.proj.bias.device.type != "meta":
             self.proj.bias[self.q_cols + self.kv_cols:].zero_()           # the gate logits have no bias
         if qk_norm not in (None, "head", "projection"):
             raise ValueError(f"qk_norm '{qk_norm}' is none of None, 'head', 'projection'")
@@ -82,6 +94,24 @@ class GatedWindowAttention(Mixer):
         # the norm over a whole projection has a weight per column; the norm per head has none here
         self.q_norm_w = torch.empty((self.q_cols,), **f32) if qk_norm == "projection" else None
         self.k_norm_w = torch.empty((kv_heads * head_dim,), **f32) if qk_norm == "projection" and own_kv else None
+        if head_norm_weight:
+            if qk_norm != "head":
+                raise ValueError("a weight of the head's size belongs to the norm per head")
+            self.q_norm_w = torch.empty((head_dim,), **f32)
+            self.k_norm_w = torch.empty((head_dim,), **f32) if own_kv else None
+        self.q_temp = (float(q_temp[0]), int(q_temp[1])) if q_temp else None
+        self.rel = self.rel_bucket = None
+        if distance_table:
+            rows, far = int(distance_table[0]), int(distance_table[1])
+            half = rows // 2
+            if rows < 2 or far <= half:
+                raise ValueError(f"a table of {rows} distance terms up to distance {far}: it needs two rows at least and far beyond rows / 2")
+            import math
+            buckets = [n if n < half else min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
+                       for n in range(far + 1)]
+            self.rel = torch.empty((rows, heads), **f32)
+            self.rel_bucket = torch.tensor(buckets, dtype=torch.int32).to(device) if torch.device(device).type != "meta" else \
+                torch.empty((far + 1,), dtype=torch.int32, device=device)
         self.r1 = torch.empty((heads,), **f32) if distance_bias else None
         self.r2 = torch.empty((heads,), **f32) if distance_bias else None
         self.pb = torch.empty((heads,), **f32) if head_bias else None
@@ -90,11 +120,11 @@ class GatedWindowAttention(Mixer):
         if head_sink and weighting != "softmax_sink":
             raise ValueError("a learned number per head for the denominator's extra term belongs to the weighting 'softmax_sink'")
         self.sink = torch.empty((heads,), **f32) if head_sink else None
-        self.score = ops.ScoreOptions(softcap, self.r1, self.r2, self.pb, weighting, self.sink)
-        self._scored = bool(softcap) or distance_bias or weighting != "softmax"
+        self.score = ops.ScoreOptions(softcap, self.r1, self.r2, self.pb, weighting, self.sink, self.rel, self.rel_bucket)
+        self._scored = bool(softcap) or distance_bias or weighting != "softmax" or self.rel is not None
         # checkpoint names of what the options add, after the projections' own names
         self.extra_names = dict(bias=".b", q_norm=names[0] + ".norm", k_norm=names[1] + ".norm", r1="r1", r2="r2", head_bias="pb",
-                                sink="sink")
+                                sink="sink", rel="rel")
         self.extra_names.update(extra_names or {})
 
     def cache_spec(self) -> PagedKVSpec:
@@ -107,7 +137,7 @@ class GatedWindowAttention(Mixer):
         if self.own_kv:
             k_end = self.q_cols + self.kv_heads * self.head_dim
             slots += [WeightSlot(p + nk, w[self.q_cols:k_end]), WeightSlot(p + nv, w[k_end:self.q_cols + self.kv_cols])]
-        if self.head_gate:
+        if self.gate_cols:
             slots.append(WeightSlot(p + ng, w[self.q_cols + self.kv_cols:]))
         slots.append(WeightSlot(p + no, self.out.weight))
         x = self.extra_names
@@ -130,6 +160,8 @@ class GatedWindowAttention(Mixer):
             slots.append(WeightSlot(p + x["head_bias"], self.pb, "bias"))
         if self.sink is not None:
             slots.append(WeightSlot(p + x["sink"], self.sink, "bias"))
+        if self.rel is not None:
+            slots.append(WeightSlot(p + x["rel"], self.rel, "bias"))
         return slots
 
     def forward(self, x: torch.Tensor, batch, cache, residual: Optional[torch.Tensor] = None) -> Optional[ops.Partials]:
@@ -142,12 +174,12 @@ class GatedWindowAttention(Mixer):
         table = batch.block_table(cache.group)
         ops.attn_prepare_ex(fused, self.q_norm_w, self.k_norm_w, self.qk_norm, self.norm_eps, batch.positions, batch.seq_of_token, table,
                             cache.page_size, cache.k, cache.v, q, gate, self.heads, self.kv_heads, self.head_dim, self.v_head_dim,
-                            self.own_kv, v_norm=self.v_norm, rotation=self.rotation)
+                            self.own_kv, v_norm=self.v_norm, rotation=self.rotation, q_temp=self.q_temp)
         score = self.score if self._scored else None
         a = torch.empty((T, self.heads * self.v_head_dim), dtype=self.dtype, device=x.device)
         G = self.heads // self.kv_heads
         if self.dtype == torch.bfloat16 and not self.force_plain and self.tcgen05 and self.head_dim == self.v_head_dim == 128 and \
-                gate is None and self.keep_first == 0 and not batch.captured and batch.max_count * G > self.TC_MIN_ROWS and \
+                gate is None and self.rel is None and self.keep_first == 0 and not batch.captured and batch.max_count * G > self.TC_MIN_ROWS and \
                 ops.attention_tc_supported(128, cache.page_size):
             # prompt portions of head size 128: the tcgen05 kernel, rows in tiles of 256 per request
             tile_seq, tile_row0 = ops.row_tiles(batch, G, 256)
@@ -172,4 +204,6 @@ class GatedWindowAttention(Mixer):
         else:           # float32, and head sizes that are no multiple of 8
             ops.attention_plain_ex(q, cache.k, cache.v, batch.positions, batch.seq_of_token, table, cache.page_size, a, self.heads,
                                    self.kv_heads, self.head_dim, self.v_head_dim, self.window, self.keep_first, gate, self.scale, score)
+        if self.element_gate:
+            ops.gate_columns_mul(a, fused, self.q_cols + self.kv_cols)
         return self.out.forward(a, residual=residual)      # without bias and with many tokens the product adds itself to the stream

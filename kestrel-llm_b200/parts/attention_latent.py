@@ -10,7 +10,15 @@ With h the mixer's input, H heads, d query/key dimensions and dv value dimension
     p   = softmax_j(q_n . k_nj * scale)         over the window: query i sees key j if 0 <= i - j < window (0: all)
     y   = W_o concat_n( sigmoid(W_g h)_n * sum_j p_j v_nj )
 
-Heads are not rotated.  Since q_n . k_nj = (Uk_n^T q_n) . c_j and sum_j p_j v_nj = Uv_n sum_j p_j c_j,
+Heads are not rotated unless the mixer is built with ``rot_dim`` > 0: a head's query then has ``rot_dim`` more dimensions behind
+its ``d`` unrotated ones, W_dkv has ``rot_dim`` more rows behind the latent's - one key part that ALL heads share, not normed -,
+both are turned by position as ``position`` (a `PositionEncoding` with a `rotary()`) says, and the score is
+(q_n[:d] . k_nj + q_n[d:] . kr_j) * scale.  The cache row of a token is then [c | kr], and the query that meets it
+[Uk_n^T q_n[:d] | q_n[d:]]: attention still runs over the cache rows themselves, as one key/value head of kv_rank + rot_dim
+numbers whose first kv_rank are the value (the mixed rows' last rot_dim columns are not used).  ``element_gate``: the gate is a
+number per element of the concatenated heads instead of one per head.
+
+Since q_n . k_nj = (Uk_n^T q_n) . c_j and sum_j p_j v_nj = Uv_n sum_j p_j c_j,
 attention runs over the cached latents themselves as ONE key/value head of size kv_rank shared by
 all query heads (`PagedKVSpec.values_are_keys`): the queries are taken into the latent space by a
 head-wise product before it, the mixed latents out of it by another one afterwards.  W_dq, W_dkv
@@ -44,15 +52,23 @@ class LatentAttention(Mixer):
 
     def __init__(self, width: int, heads: int, head_dim: int, v_head_dim: int, q_rank: int, kv_rank: int, dtype: torch.dtype, device,
                  prefix: str, scale: float, norm_eps: float, window: int = 0, head_gate: bool = True,
-                 names=("dq", "uq", "dkv", "uk", "uv", "g", "o")):
-        if kv_rank > 256:
-            raise ValueError(f"a cached latent of {kv_rank} numbers: the attention kernels take head sizes up to 256")
+                 names=("dq", "uq", "dkv", "uk", "uv", "g", "o"), rot_dim: int = 0, position=None, element_gate: bool = False):
+        if kv_rank + rot_dim > 256:
+            raise ValueError(f"a cached row of {kv_rank} + {rot_dim} numbers: the attention kernels take head sizes up to 256")
+        if element_gate and head_gate:
+            raise ValueError("a gate per head or a gate per element, not both")
+        self.rot_dim, self.element_gate = int(rot_dim), bool(element_gate)
+        self.rotation = position.rotary() if position is not None and rot_dim else None
+        if self.rotation is not None and self.rotation.dim > rot_dim:
+            raise ValueError(f"{self.rotation.dim} rotated dimensions exceed the rotated part of {rot_dim}")
+        self.row = kv_rank + self.rot_dim                      # what the cache keeps of a token
         self.width, self.heads, self.head_dim, self.v_head_dim = width, heads, head_dim, v_head_dim
         self.q_rank, self.kv_rank, self.window = q_rank, kv_rank, int(window)
         self.scale, self.norm_eps, self.head_gate = float(scale), float(norm_eps), head_gate
         self.prefix, self.names, self.dtype = prefix, names, dtype
-        self.down = Linear(width, q_rank + kv_rank + (heads if head_gate else 0), dtype, device)
-        self.up_q = Linear(q_rank, heads * head_dim, dtype, device)
+        self.gate_cols = heads if head_gate else (heads * v_head_dim if element_gate else 0)
+        self.down = Linear(width, q_rank + self.row + self.gate_cols, dtype, device)
+        self.up_q = Linear(q_rank, heads * (head_dim + self.rot_dim), dtype, device)
         self.up_kv = Linear(kv_rank, heads * (head_dim + v_head_dim), dtype, device)     # rows [k | v]: one product where both are expanded
         self.up_k_w = self.up_kv.weight[:heads * head_dim]                  # used transposed, head by head
         self.up_v_w = self.up_kv.weight[heads * head_dim:]
@@ -61,16 +77,16 @@ class LatentAttention(Mixer):
         self.kv_norm_w = torch.empty((kv_rank,), dtype=torch.float32, device=device)
 
     def cache_spec(self) -> PagedKVSpec:
-        return PagedKVSpec(1, self.kv_rank, self.window, 0, self.kv_rank, values_are_keys=True)
+        return PagedKVSpec(1, self.row, self.window, 0, self.row, values_are_keys=True)
 
     def weight_slots(self) -> List[WeightSlot]:
         p, (dq, uq, dkv, uk, uv, g, o) = self.prefix, self.names
-        w, r = self.down.weight, self.q_rank + self.kv_rank
+        w, r = self.down.weight, self.q_rank + self.row
         slots = [WeightSlot(p + dq, w[:self.q_rank]), WeightSlot(p + dkv, w[self.q_rank:r]),
                  WeightSlot(p + dq + ".norm", self.q_norm_w, "norm"), WeightSlot(p + dkv + ".norm", self.kv_norm_w, "norm"),
                  WeightSlot(p + uq, self.up_q.weight), WeightSlot(p + uk, self.up_k_w), WeightSlot(p + uv, self.up_v_w),
                  WeightSlot(p + o, self.out.weight)]
-        if self.head_gate:
+        if self.gate_cols:
             slots.append(WeightSlot(p + g, w[r:]))
         return slots
 
@@ -81,22 +97,31 @@ class LatentAttention(Mixer):
         gate = torch.empty((T, H), dtype=torch.float32, device=x.device) if self.head_gate else None
         table = batch.block_table(cache.group)
         expand = (self.dtype == torch.bfloat16 and not self.force_plain and self.expand_prompts and self.head_dim == self.v_head_dim == 128
-                  and not batch.captured and batch.max_count > self.EXPAND_MIN_TOKENS and all(s == 0 for s in batch.starts)
+                  and self.rot_dim == 0 and not self.element_gate and not batch.captured and batch.max_count > self.EXPAND_MIN_TOKENS and all(s == 0 for s in batch.starts)
                   and ops.attention_tc_supported(128, cache.page_size))
         c_rows = torch.empty((T, R), dtype=self.dtype, device=x.device) if expand else None
         ops.latent_prepare(fused, self.q_norm_w, self.kv_norm_w, self.norm_eps, batch.positions, batch.seq_of_token, table, cache.page_size,
-                           cache.k, cq, gate, kv_out=c_rows)
-        q = self.up_q.forward(cq).reduce(self.dtype)                           # [T, H d]
+                           cache.k, cq, gate, kv_out=c_rows, rot_cols=self.rot_dim, rotation=self.rotation)
+        q = self.up_q.forward(cq).reduce(self.dtype)                           # [T, H (d + rot_dim)]
         if expand:
             return self._forward_expanded(q, c_rows, gate, batch, cache.page_size, residual)
-        q_lat = ops.head_gemm(q, self.up_k_w, H, w_kn=True)                    # [T, H kv_rank]: Uk_n^T q_n
-        a = torch.empty((T, H * R), dtype=self.dtype, device=x.device)
-        if self.dtype == torch.bfloat16 and not self.force_plain and ops.attention_window_supported(R, R, H, 1):
-            ops.attention_window(q_lat, cache.k, cache.k, batch, table, cache.page_size, a, H, 1, R, R, self.window, 0, gate, self.scale)
+        D, d = self.row, self.head_dim
+        if self.rot_dim:
+            # a head's query in the space of the cache rows: [Uk_n^T q_n[:d] | q_n[d:] turned by position]
+            q_lat = torch.empty((T, H * D), dtype=self.dtype, device=x.device)
+            ops.head_gemm(q, self.up_k_w, H, w_kn=True, out=q_lat, x_head_stride=d + self.rot_dim, out_head_stride=D)
+            ops.latent_rotate_queries(q, H, d, self.rot_dim, q_lat, R, batch.positions, self.rotation)
         else:
-            ops.attention_plain_ex(q_lat, cache.k, cache.k, batch.positions, batch.seq_of_token, table, cache.page_size, a, H, 1, R, R,
+            q_lat = ops.head_gemm(q, self.up_k_w, H, w_kn=True)                # [T, H kv_rank]: Uk_n^T q_n
+        a = torch.empty((T, H * D), dtype=self.dtype, device=x.device)
+        if self.dtype == torch.bfloat16 and not self.force_plain and ops.attention_window_supported(D, D, H, 1):
+            ops.attention_window(q_lat, cache.k, cache.k, batch, table, cache.page_size, a, H, 1, D, D, self.window, 0, gate, self.scale)
+        else:
+            ops.attention_plain_ex(q_lat, cache.k, cache.k, batch.positions, batch.seq_of_token, table, cache.page_size, a, H, 1, D, D,
                                    self.window, 0, gate, self.scale)
-        o = ops.head_gemm(a, self.up_v_w, H, w_kn=False)                       # [T, H dv]: Uv_n (mixed latent)
+        o = ops.head_gemm(a, self.up_v_w, H, w_kn=False, x_head_stride=D)      # [T, H dv]: Uv_n (mixed latent)
+        if self.element_gate:
+            ops.gate_columns_mul(o, fused, self.q_rank + self.row)
         return self.out.forward(o, residual=residual)      # many tokens: the product adds itself to the stream
 
     def _forward_expanded(self, q, c_rows, gate, batch, page: int, residual):

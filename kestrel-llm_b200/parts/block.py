@@ -59,7 +59,8 @@ class PreNormBlock(Block):
 
 class ParallelBlock(Block):
     """One norm whose output both sublayers read: h = norm(x); x += mixer(h) + ffn(h); then an
-    optional per-layer token input, x += side(x, token).  The feed-forward may be absent."""
+    optional per-layer token input, x += side(x, token).  The feed-forward may be absent; it may also hand
+    on two products (routed experts and an expert every token takes), which are added in its order."""
 
     def __init__(self, norm: Norm, mixer: Mixer, ffn: Optional[FeedForward], side, dtype: torch.dtype):
         self.norm, self.mixer, self.ffn, self.side = norm, mixer, ffn, side
@@ -76,11 +77,12 @@ class ParallelBlock(Block):
         h = self.norm.add_forward(residual, pending, self.dtype)
         a = self.mixer.forward(h, batch, cache)
         f = self.ffn.forward(h, batch) if self.ffn is not None else None
+        f, f2 = f if isinstance(f, tuple) else (f, None)
         if self.side is None:
-            ops.add_two(residual, a, f, None)
+            ops.add_two(residual, a, f, None, f2)
             return residual, None
         x = torch.empty(residual.shape, dtype=self.dtype, device=residual.device)
-        ops.add_two(residual, a, f, x)
+        ops.add_two(residual, a, f, x, f2)
         self.side.add_forward(residual, x, batch)
         return residual, None
 

@@ -17,17 +17,20 @@ from .base import Part, WeightSlot
 class TokenEmbedding(Part):
     graph_safe = True
 
-    def __init__(self, vocab: int, width: int, dtype: torch.dtype, device, weight_name: str):
+    def __init__(self, vocab: int, width: int, dtype: torch.dtype, device, weight_name: str, scale: float = 1.0):
         self.vocab, self.width = vocab, width
         self.weight = torch.empty((vocab, width), dtype=dtype, device=device)
         self.weight_name = weight_name
+        self.scale = float(scale)              # x = E[token] * scale
+        if self.scale != 1.0:
+            self.emit = None                   # the step program's embedding has no factor: such a model walks its parts
 
     def weight_slots(self) -> List[WeightSlot]:
         return [WeightSlot(self.weight_name, self.weight)]
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         out = torch.empty((token_ids.shape[0], self.width), dtype=torch.float32, device=token_ids.device)
-        ops.embed(self.weight, token_ids, out)
+        ops.embed(self.weight, token_ids, out, self.scale)
         return out
 
     def add_forward(self, token_ids: torch.Tensor, x: torch.Tensor) -> None:
@@ -36,6 +39,22 @@ class TokenEmbedding(Part):
 
     def emit(self, prog) -> int:
         return prog.embed(self.weight)
+
+
+class StreamRows(Part):
+    """Learned vectors of the stream's width, one of which is added to every token of the stream in front of a
+    layer call (`LayerCall.add_row`): float32 [rows, width]."""
+    graph_safe = True
+
+    def __init__(self, rows: int, width: int, device, weight_name: str):
+        self.weight = torch.empty((rows, width), dtype=torch.float32, device=device)
+        self.weight_name = weight_name
+
+    def weight_slots(self) -> List[WeightSlot]:
+        return [WeightSlot(self.weight_name, self.weight, "bias")]
+
+    def add_forward(self, row: int, x: torch.Tensor) -> None:
+        ops.add_row(x, self.weight[row])
 
 
 class LMHead(Part):

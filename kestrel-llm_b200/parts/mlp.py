@@ -42,13 +42,13 @@ class GatedMLP(FeedForward):
 
 class DenseMLP(FeedForward):
     """Feed-forward without a gate: y = W_down act(W_up x), ``activation`` "relu2" (the square of
-    relu), "silu" or "tanh"."""
+    relu), "silu", "tanh", "gelu" (the exact one, with erf) or "gelu_tanh"."""
     graph_safe = True
 
     def __init__(self, width: int, intermediate: int, dtype: torch.dtype, device, prefix: str, activation: str = "relu2",
                  names=("up", "down")):
-        if activation not in ("relu2", "silu", "tanh"):
-            raise ValueError(f"activation '{activation}' has no kernel; one of 'relu2', 'silu', 'tanh'")
+        if activation not in ("relu2", "silu", "tanh", "gelu", "gelu_tanh"):
+            raise ValueError(f"activation '{activation}' has no kernel; one of 'relu2', 'silu', 'tanh', 'gelu', 'gelu_tanh'")
         self.width, self.intermediate, self.activation = width, intermediate, activation
         self.prefix, self.names, self.dtype = prefix, names, dtype
         self.up = Linear(width, intermediate, dtype, device)

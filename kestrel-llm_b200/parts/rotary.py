@@ -38,6 +38,35 @@ class FrequencyScaling:
         return np.where(wave < self.original / self.high, f, np.where(wave > self.original / self.low, f / self.factor, blended))
 
 
+@dataclass(frozen=True)
+class RampScaling:
+    """Stretching of a rotary encoding by a ramp over the pair index (the scheme published as YaRN): with
+    where(t) = dims ln(original / (2 pi t)) / (2 ln base) the pair index whose wavelength fits t times into the original
+    context, lo = max(floor(where(fast)), 0), hi = min(ceil(where(slow)), dims - 1) and ramp_i = clamp((i - lo) /
+    max(hi - lo, 0.001), 0, 1), pair i turns with f_i / factor * ramp_i + f_i (1 - ramp_i).  `magnitude` is the factor the
+    scheme puts on cos and sin, 0.1 ln(factor) + 1."""
+    factor: float
+    original: float
+    fast: float
+    slow: float
+    dims: int
+    base: float
+
+    def apply(self, freq: np.ndarray) -> np.ndarray:
+        f = np.asarray(freq, dtype=np.float64)
+
+        def where(turns: float) -> float:
+            return self.dims * math.log(self.original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.base))
+        lo = max(math.floor(where(self.fast)), 0)
+        hi = min(math.ceil(where(self.slow)), self.dims - 1)
+        ramp = np.clip((np.arange(f.shape[0], dtype=np.float64) - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        return f / self.factor * ramp + f * (1.0 - ramp)
+
+    @property
+    def magnitude(self) -> float:
+        return 0.1 * math.log(self.factor) + 1.0
+
+
 class RotaryHalf(PositionEncoding):
     graph_safe = True
 
