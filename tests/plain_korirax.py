@@ -203,21 +203,38 @@ def ff_dense(h, w, p):
     return (g * sigmoid(g) * (h @ w[p + "up"].T)) @ w[p + "down"].T
 
 
+MARGINS = None      # a list, while a caller wants to know how close the routers' calls were: (token, margin) of every call
+
+
+def _margin(sorted_desc, kept):
+    """Per row: the gap between the last value that is kept and the best that is not (inf where all are kept)."""
+    if kept >= sorted_desc.shape[-1]:
+        return np.full(sorted_desc.shape[0], np.inf)
+    gap = sorted_desc[:, kept - 1] - sorted_desc[:, kept]
+    return np.where(np.isnan(gap), np.inf, gap)        # -inf minus -inf: closed experts on both sides
+
+
 def route(h, w, p, r):
     """Chosen experts [T, top] and their weights."""
     E, top = r["experts"], r["top"]
     s = sigmoid(h @ w[p + "router"].T)
     choice = s + w[p + "correction"]
     groups = r.get("groups")
+    margin = np.full(h.shape[0], np.inf)
     if groups and groups["count"] > 1:
         per = E // groups["count"]
         byg = choice.reshape(-1, groups["count"], per)
         gs = np.sort(byg, axis=-1)[..., -2:].sum(axis=-1) if per > 1 else byg[..., 0]
         keep = np.argsort(-gs, axis=-1, kind="stable")[:, :groups["keep"]]
+        margin = np.minimum(margin, _margin(-np.sort(-gs, axis=-1), groups["keep"]))
         allowed = np.zeros(gs.shape, dtype=bool)
         np.put_along_axis(allowed, keep, True, axis=-1)
         choice = np.where(np.repeat(allowed, per, axis=-1), choice, -np.inf)
     ids = np.argsort(-choice, axis=-1, kind="stable")[:, :top]
+    if MARGINS is not None:
+        with np.errstate(invalid="ignore"):
+            margin = np.minimum(margin, _margin(-np.sort(-choice, axis=-1), top))
+        MARGINS.extend(enumerate(margin))
     ws = np.take_along_axis(s, ids, axis=-1)
     ws = ws / (ws.sum(axis=-1, keepdims=True) + 1e-20) * r.get("scale", 1.0)
     return ids, ws
