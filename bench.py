@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl ours|reference]
     python bench.py --workload mix14b | 32b
-    python bench.py --workload zidivik | tidavik | toredra [--size a|b]
+    python bench.py --workload zidivik | tidavik | toredra | korirax [--size a|b]
 
 Default run (the headline): decode tokens a second at batch 8, at batch 1 and 64, prefill of
 2,048 tokens, and the same decode through the Python entry point with host tokens in and out.
@@ -37,6 +37,11 @@ and window.
 forget-gate recurrence, a generalised delta rule, gated and twice-normed sublayers, an ungated feed-forward with
 the square of relu) the same way, beside the Qwen3 dense decoder of equal width, heads, depth, vocabulary and
 feed-forward weights.
+
+`--workload korirax`: the Korirax decoder (attention with a table of distance terms, a query temperature and a gate per
+element; attention over cached latents with a rotated key part that all heads share; a gated diagonal recurrence; dense
+gated feed-forward and routed experts with a sigmoid router, groups and a shared expert; a token input per layer) the same
+way, beside the Qwen3 dense decoder of equal width, heads, depth, vocabulary and active feed-forward weights.
 
 Timing: CUDA events on the launching stream around exactly K steps after W warm-up steps, with
 a synchronize on both sides.  Every step streams all weights (15 GB) and the live requests'
@@ -323,11 +328,38 @@ def toredra_raw(z):
             "logit_scale": 0.5, "logit_softcap": 30.0, "layers": layers}
 
 
+KORIRAX_SIZES = {
+    # width, attention heads / kv heads x head sizes, rows of the distance table, latent heads x (unrotated + rotated) / value size and ranks,
+    # recurrence channels and blocks, dense feed-forward, experts x ff (top 4 of groups) and the shared expert, token input, vocab
+    "a": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, rows=32, l_heads=16, l_dim=128, l_rot=64, l_vdim=128, q_rank=768, kv_rank=192,
+              channels=2048, blocks=16, ff=6144, experts=32, top=4, e_ff=768, groups=4, keep=2, shared=768, side=128, vocab=32000),
+    "b": dict(width=4096, heads=32, kv_heads=8, dim=128, vdim=128, rows=32, l_heads=32, l_dim=128, l_rot=64, l_vdim=128, q_rank=1536, kv_rank=192,
+              channels=4096, blocks=16, ff=12288, experts=64, top=4, e_ff=1024, groups=8, keep=4, shared=1024, side=256, vocab=64000),
+}
+
+
+def korirax_raw(z):
+    att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5, "bias_max": 4096,
+           "bias_rows": z["rows"], "q_temp": {"coef": 0.1, "every": 1024}}
+    lat = {"heads": z["l_heads"], "dim": z["l_dim"], "rot_dim": z["l_rot"], "vdim": z["l_vdim"], "q_rank": z["q_rank"], "kv_rank": z["kv_rank"],
+           "scale": (z["l_dim"] + z["l_rot"]) ** -0.5,
+           "rot": {"dims": z["l_rot"], "base": 10000.0, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+    rec = {"width": z["channels"], "blocks": z["blocks"], "conv": 4}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["e_ff"]}, "router": {"experts": z["experts"], "top": z["top"], "scale": 2.5,
+                                                                  "groups": {"count": z["groups"], "keep": z["keep"]}}, "shared": {"ff": z["shared"]}}
+    layers = [{"type": "attention", "mixer": att, "mlp": dense}, {"type": "latent_attention", "mixer": lat, "mlp": moe},
+              {"type": "rglru", "mixer": rec, "mlp": dense}, {"type": "latent_attention", "mixer": lat, "mlp": moe}]
+    return {"architecture": "Korirax", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "token_side": {"dim": z["side"]}, "max_positions": 8192, "layers": layers}
+
+
 def run_zidivik(args) -> int:
-    """Prefill and decode of the Zidivik, the Tidavik or the Toredra decoder at real layer sizes, beside the Qwen3 dense decoder of equal size."""
+    """Prefill and decode of the Zidivik, the Tidavik, the Toredra or the Korirax decoder at real layer sizes, beside the Qwen3 dense decoder of equal size."""
     import numpy as np
     import torch
     from kestrel_llm_b200.config import EngineOptions, Qwen3Config, TidavikConfig, ToredraConfig, ZidivikConfig
+    from kestrel_llm_b200.config.korirax_config import KoriraxConfig
     from kestrel_llm_b200.config.registry import resolve_architecture
     from kestrel_llm_b200.csrc import ops
     from kestrel_llm_b200.engine import Engine, Entry
@@ -335,8 +367,8 @@ def run_zidivik(args) -> int:
 
     dev = "cuda:0"
     torch.cuda.set_device(0)
-    tidavik, toredra = args.workload == "tidavik", args.workload == "toredra"
-    z = (TOREDRA_SIZES if toredra else TIDAVIK_SIZES if tidavik else ZIDIVIK_SIZES)[args.size]
+    tidavik, toredra, korirax = args.workload == "tidavik", args.workload == "toredra", args.workload == "korirax"
+    z = (KORIRAX_SIZES if korirax else TOREDRA_SIZES if toredra else TIDAVIK_SIZES if tidavik else ZIDIVIK_SIZES)[args.size]
     T, B, CTX = args.prefill_tokens, args.batch, 2048
     W, K = max(3, args.warmup), max(1, min(args.steps, 32))
     pk = peaks()
@@ -346,7 +378,8 @@ def run_zidivik(args) -> int:
                    "gate_up_swiglu", "moe_route", "moe_experts", "delta_conv_silu", "delta_gates", "delta_scan", "delta_out", "partial_columns",
                    "add_two", "gelu_table_mul", "add_normed", "embed", "add_sinusoid", "linear_add_into", "latent_prepare", "head_gemm", "attention_tc",
                    "forget_gates", "removal_gates", "recurrence_scan", "head_norm_gate", "combine_normed", "add_gated_normed", "partial_columns_act",
-                   "embed_add", "logit_scale_cap", "linear_act"]
+                   "embed_add", "logit_scale_cap", "linear_act", "rglru_branches", "rglru_scan", "moe_route_sigmoid", "moe_experts_ungated",
+                   "gate_columns_mul", "latent_rotate_queries", "add_row"]
 
     def measure(cfg, label):
         model = resolve_architecture(cfg.architecture).build(cfg, torch.bfloat16, dev)
@@ -361,6 +394,8 @@ def run_zidivik(args) -> int:
                     r.f_bias.normal_(2.0, 1.0)
                 if hasattr(r, "w0"):
                     r.w0.normal_(-1.0, 1.0)
+            if hasattr(m, "lam"):               # decays that keep a state for hundreds of tokens
+                m.lam.normal_(-4.0, 1.0)
         opts = EngineOptions(dtype="bfloat16", page_size=args.page_size, batch_max=B + 1, max_model_len=CTX + T + 64,
                              max_tokens=B * (CTX + 128) + T + 64, max_step_tokens=max(T, B), prefill_batch=T)
         engine = Engine(model, opts)
@@ -460,19 +495,49 @@ def run_zidivik(args) -> int:
                 "decode_batch": B, "decode_context": CTX, "decode_ms": round(1000 * dec, 4), "decode_tok_s": round(B / dec, 1),
                 "launches_per_decode_step": int(launches), "device_us_per_operation": split}
 
-    raw = toredra_raw(z) if toredra else tidavik_raw(z) if tidavik else zidivik_raw(z)
-    zc = (ToredraConfig if toredra else TidavikConfig if tidavik else ZidivikConfig).from_dict(raw)
+    raw = korirax_raw(z) if korirax else toredra_raw(z) if toredra else tidavik_raw(z) if tidavik else zidivik_raw(z)
+    zc = (KoriraxConfig if korirax else ToredraConfig if toredra else TidavikConfig if tidavik else ZidivikConfig).from_dict(raw)
     L = len(raw["layers"])
     dense_raw = dict(QWEN3_8B, num_hidden_layers=L, hidden_size=z["width"], num_attention_heads=z["heads"],
                      num_key_value_heads=z["kv_heads"], head_dim=z["dim"],
-                     intermediate_size=z["ff"] * 2 // 3 if toredra else z["ff"] if tidavik else z["top"] * z["ff"],
+                     intermediate_size=(z["ff"] + (z["top"] * z["e_ff"] + z["shared"]) * 2 // 3) // 2 if korirax else
+                     z["ff"] * 2 // 3 if toredra else z["ff"] if tidavik else z["top"] * z["ff"],
                      vocab_size=z["vocab"], max_position_embeddings=8192)
     if tidavik:                              # the dense model's layers look through the same window
         dense_raw.update(sliding_window=z["window"], use_sliding_window=True, layer_types=["sliding_attention"] * L)
     qc = Qwen3Config.from_dict(dense_raw)
-    ours = measure(zc, "Toredra" if toredra else "Tidavik" if tidavik else "Zidivik")
+    ours = measure(zc, "Korirax" if korirax else "Toredra" if toredra else "Tidavik" if tidavik else "Zidivik")
     dense = measure(qc, "Qwen3 dense, equal size" + (" and window" if tidavik else ""))
     clocks.close()
+    if korirax:
+        D, H, G, d, dv, ff = z["width"], z["heads"], z["kv_heads"], z["dim"], z["vdim"], z["ff"]
+        LH, ld, lr, lv, qr, kr, C = z["l_heads"], z["l_dim"], z["l_rot"], z["l_vdim"], z["q_rank"], z["kv_rank"], z["channels"]
+        att_w = D * (H * d + G * (d + dv) + H * dv) + H * dv * D
+        lat_w = D * (qr + kr + lr + LH * lv) + qr * LH * (ld + lr) + LH * ld * kr + LH * lv * kr + LH * lv * D
+        rec_w = D * 2 * C + 2 * C * (C // z["blocks"]) + C * D
+        moe_active = 2 * z["e_ff"] * D * z["top"] + 2 * z["shared"] * D + z["experts"] * D
+        moe_touched = 2 * z["e_ff"] * D * min(z["experts"], B * z["top"]) + 2 * z["shared"] * D + z["experts"] * D      # a decode step of B tokens
+        side_w = L * 2 * z["side"] * D
+        mixers = att_w + 2 * lat_w + rec_w
+        active = mixers + 2 * 3 * ff * D + 2 * moe_active + side_w
+        touched = mixers + 2 * 3 * ff * D + 2 * moe_touched + side_w + z["vocab"] * D
+        row = kr + lr
+        # products, causal attention (half of the T x T scores; the latent layers over rows of kv_rank + rot_dim for keys and values alike)
+        flops_prefill = 2.0 * T * active + 2.0 * H * (d + dv) * T * T / 2 + 2 * 2.0 * LH * 2 * row * T * T / 2
+        cache_bytes = 2.0 * B * CTX * (G * (d + dv) + 2 * row)
+        rec = {"metric": f"Korirax prefill tokens/s at size {args.size}, bf16, beside Qwen3 dense of equal size", "value": ours["prefill_tok_s"],
+               "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ours["prefill_ms"], "higher_is_better": True,
+               "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "impl": "ours", "workload": "korirax",
+               "data": "synthetic: random weights, uniform random token ids, cache of the context filled with random values",
+               "config": dict(z, layers=[l["type"] + "+" + l["mlp"]["kind"] for l in raw["layers"]], page_size=args.page_size, peaks=pk["source"],
+                              parallelism="single GPU"),
+               "korirax": ours, "dense": dense,
+               "ratio_to_dense": {"prefill": round(ours["prefill_tok_s"] / dense["prefill_tok_s"], 3), "decode": round(ours["decode_tok_s"] / dense["decode_tok_s"], 3)},
+               "prefill_flops_frac_of_peak": round(flops_prefill / (ours["prefill_ms"] / 1000.0) / (pk["bf16_tflops"] * 1e12), 4),
+               "decode_bytes_frac_of_hbm": round((2.0 * touched + cache_bytes) / (ours["decode_ms"] / 1000.0) / (pk["hbm_gbs"] * 1e9), 4),
+               "gpu_launches": ours["launches_per_decode_step"] * K, "clocks": clocks.summary()}
+        print(json.dumps(rec))
+        return 0
     if toredra:
         D, H, G, d, dv, ff = z["width"], z["heads"], z["kv_heads"], z["dim"], z["vdim"], z["ff"]
         rn, rv, dn = z["r_heads"] * z["r_dim"], z["r_heads"] * z["r_vdim"], z["d_heads"] * z["d_dim"]
@@ -549,10 +614,10 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (default 16)")
     ap.add_argument("--context", type=int, default=CONTEXT, help="context length at which the decode steps end (default 4096)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="tokens of the prefill step (default 2048)")
-    ap.add_argument("--workload", default="decode8b", choices=["decode8b", "mix14b", "32b", "zidivik", "tidavik", "toredra"],
-                    help="decode8b: the headline run; mix14b / 32b: whole workloads through the scheduler; zidivik / tidavik / toredra: that decoder "
+    ap.add_argument("--workload", default="decode8b", choices=["decode8b", "mix14b", "32b", "zidivik", "tidavik", "toredra", "korirax"],
+                    help="decode8b: the headline run; mix14b / 32b: whole workloads through the scheduler; zidivik / tidavik / toredra / korirax: that decoder "
                          "at real layer sizes beside Qwen3 dense of equal size")
-    ap.add_argument("--size", default="a", choices=sorted(ZIDIVIK_SIZES), help="layer sizes of --workload zidivik / tidavik / toredra")
+    ap.add_argument("--size", default="a", choices=sorted(ZIDIVIK_SIZES), help="layer sizes of --workload zidivik / tidavik / toredra / korirax")
     ap.add_argument("--requests", type=int, default=0, help="requests of a workload (0: 32 for mix14b, 16 for 32b)")
     ap.add_argument("--generate", type=int, default=0, help="tokens to generate per request of a workload (0: 256 / 128)")
     ap.add_argument("--step-tokens", type=int, default=2048,
@@ -564,7 +629,7 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py: this engine runs on ONE GPU; --gpus {args.gpus} is not supported (no multi-GPU path exists)")
         return 2
-    if args.workload in ("zidivik", "tidavik", "toredra"):
+    if args.workload in ("zidivik", "tidavik", "toredra", "korirax"):
         return run_zidivik(args)
     if args.workload != "decode8b":
         return run_workload(args)

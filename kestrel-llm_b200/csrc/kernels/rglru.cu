@@ -20,6 +20,12 @@
 //              of this step with the loads of eight tokens in flight; 1 - a^2 is taken as -expm1(2 ln a), which keeps
 //              its digits where a is close to 1.  A token's result depends on the tokens before it alone: the same bits
 //              however the request is cut into steps and whatever else is in the batch.
+//   scan in chunks (steps that bring a request many tokens): the recurrence is linear in S, so a stretch of tokens acts
+//              on the state as S -> A S + s.  A first kernel makes (A, s) of every chunk of `chunk` tokens, a thread a
+//              (request, chunk, channel), the first chunk starting from the slot's state; a second kernel folds the
+//              chunks before its own in ascending order, then runs its own chunk from there and writes the outputs (the last
+//              chunk also the new state).  2 x T x C thread-steps instead of T sequential ones; the sums are grouped by
+//              chunk, so the result differs from the sequential kernel's by rounding.
 #include "common.cuh"
 #include <math.h>
 
@@ -123,6 +129,115 @@ rglru_scan_kernel(const float *__restrict__ y, const float *__restrict__ u, cons
         }
     }
     *sp_ = s;
+}
+
+// one token's decay and drive
+__device__ __forceinline__ void rg_token(float zr, float zi, float uu, float neg, float &a, float &b) {
+    const float log_a = neg * rg_sigmoid(zr);
+    a = expf(log_a);
+    b = sqrtf(-expm1f(2.0f * log_a)) * (rg_sigmoid(zi) * uu);
+}
+
+// sums [nseq, chunks, 2, C]: a chunk's action on the state, S -> A S + s (the first chunk's s starts from the slot's state)
+__global__ void __launch_bounds__(128)
+rglru_chunk_sums_kernel(const float *__restrict__ u, const float *__restrict__ gr, const float *__restrict__ gi, const float *__restrict__ r_bias,
+                        const float *__restrict__ i_bias, const float *__restrict__ lam, float rate, const float *__restrict__ state,
+                        size_t state_stride, const int *__restrict__ cu_seqlens, const int *__restrict__ slots, float *__restrict__ sums,
+                        int chunk, int chunks, int C) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int seq = blockIdx.z, k = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int first = cu_seqlens[seq], n_tok = cu_seqlens[seq + 1] - first;
+    const int t0 = k * chunk, t1 = min(t0 + chunk, n_tok);
+    if (t0 >= n_tok) return;
+    const float l = lam[c];
+    const float neg = -rate * (l > 20.f ? l : log1pf(expf(l)));
+    const float rb = r_bias ? r_bias[c] : 0.f, ib = i_bias ? i_bias[c] : 0.f;
+    float A = 1.f, s = k == 0 ? state[(size_t)slots[seq] * state_stride + c] : 0.f;
+    for (int t = t0; t < t1; t += RG_CHUNK) {
+        float a[RG_CHUNK], b[RG_CHUNK];
+#pragma unroll
+        for (int j = 0; j < RG_CHUNK; ++j) {
+            const size_t at = (size_t)(first + min(t + j, t1 - 1)) * C + c;
+            rg_token(gr[at] + rb, gi[at] + ib, u[at], neg, a[j], b[j]);
+            if (t + j >= t1) { a[j] = 1.f; b[j] = 0.f; }
+        }
+#pragma unroll
+        for (int j = 0; j < RG_CHUNK; ++j) {
+            s = fmaf(a[j], s, b[j]);
+            A *= a[j];
+        }
+    }
+    float *o = sums + ((size_t)seq * chunks + k) * 2 * C;
+    o[c] = k == 0 ? state[(size_t)slots[seq] * state_stride + c] : A;      // the first chunk's A is never used (it acts on nothing): the state it started from
+    o[C + c] = s;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+rglru_chunk_apply_kernel(const float *__restrict__ y, const float *__restrict__ u, const float *__restrict__ gr, const float *__restrict__ gi,
+                         const float *__restrict__ r_bias, const float *__restrict__ i_bias, const float *__restrict__ lam, float rate,
+                         float *__restrict__ state, size_t state_stride, const int *__restrict__ cu_seqlens, const int *__restrict__ slots,
+                         const float *__restrict__ sums, T *__restrict__ out, int chunk, int chunks, int C) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int seq = blockIdx.z, k = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int first = cu_seqlens[seq], n_tok = cu_seqlens[seq + 1] - first;
+    const int t0 = k * chunk, t1 = min(t0 + chunk, n_tok);
+    if (t0 >= n_tok) return;
+    const float l = lam[c];
+    const float neg = -rate * (l > 20.f ? l : log1pf(expf(l)));
+    const float rb = r_bias ? r_bias[c] : 0.f, ib = i_bias ? i_bias[c] : 0.f;
+    // The state at this chunk's start.  Chunk 0's s carries the slot's state and its A slot holds that state itself: the slot is
+    // not read here, since the last chunk's thread writes it.
+    const float *p = sums + (size_t)seq * chunks * 2 * C + c;
+    float s = k == 0 ? p[0] : p[C];
+    for (int j = 1; j < k; ++j) s = fmaf(p[(size_t)j * 2 * C], s, p[(size_t)j * 2 * C + C]);
+    for (int t = t0; t < t1; t += RG_CHUNK) {
+        float a[RG_CHUNK], b[RG_CHUNK], yy[RG_CHUNK];
+#pragma unroll
+        for (int j = 0; j < RG_CHUNK; ++j) {
+            const size_t at = (size_t)(first + min(t + j, t1 - 1)) * C + c;
+            rg_token(gr[at] + rb, gi[at] + ib, u[at], neg, a[j], b[j]);
+            yy[j] = y[at];
+        }
+#pragma unroll
+        for (int j = 0; j < RG_CHUNK; ++j) {
+            if (t + j < t1) {
+                s = fmaf(a[j], s, b[j]);
+                out[(size_t)(first + t + j) * C + c] = from_f32<T>(s * yy[j]);
+            }
+        }
+    }
+    if (t1 == n_tok) state[(size_t)slots[seq] * state_stride + c] = s;
+}
+
+// The scan in chunks of `chunk` tokens (a multiple of 8), for steps in which a request brings many tokens; max_count: the most tokens
+// of one request in this step; scratch: float32 [nseq * ceil(max_count / chunk) * 2 * C]
+KESTREL_API int kestrel_rglru_scan_chunked(const float *y, const float *u, const float *gr, const float *gi, const float *r_bias, const float *i_bias,
+                                           const float *lam, float rate, float *state, long long state_stride, const int *cu_seqlens,
+                                           const int *slots, void *out, int dtype, int nseq, int max_count, int chunk, float *scratch, int C,
+                                           cudaStream_t stream) {
+    if (nseq == 0 || max_count == 0) return 0;
+    KESTREL_REQUIRE(nseq > 0 && nseq <= 65535 && C > 0 && rate > 0.f && chunk >= 8 && chunk % 8 == 0 && max_count > 0 && scratch, "rglru_scan_chunked: bad sizes");
+    const int chunks = (max_count + chunk - 1) / chunk;
+    KESTREL_REQUIRE(chunks <= 65535, "rglru_scan_chunked: %d chunks exceed the grid", chunks);
+    dim3 grid((C + 127) / 128, chunks, nseq);
+    kestrel_launch(rglru_chunk_sums_kernel, grid, dim3(128), 0, stream, u, gr, gi, r_bias, i_bias, lam, rate, (const float *)state, (size_t)state_stride,
+                   cu_seqlens, slots, scratch, chunk, chunks, C);
+    int rc = kestrel_check_launch("rglru_chunk_sums");
+    if (rc != 0) return rc;
+    if (dtype == KESTREL_F32)
+        kestrel_launch(rglru_chunk_apply_kernel<float>, grid, dim3(128), 0, stream, y, u, gr, gi, r_bias, i_bias, lam, rate, state, (size_t)state_stride,
+                       cu_seqlens, slots, (const float *)scratch, (float *)out, chunk, chunks, C);
+    else if (dtype == KESTREL_BF16)
+        kestrel_launch(rglru_chunk_apply_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, y, u, gr, gi, r_bias, i_bias, lam, rate, state, (size_t)state_stride,
+                       cu_seqlens, slots, (const float *)scratch, (__nv_bfloat16 *)out, chunk, chunks, C);
+    else
+        return kestrel_fail(-2, "rglru_scan_chunked: unknown dtype %d", dtype);
+    return kestrel_check_launch("rglru_chunk_apply");
 }
 
 // partial: the fused product [y | x] as float32 slices, bias [2 C] or NULL; conv_w [C, taps] (last column the current token's),

@@ -1470,10 +1470,15 @@ def rglru_branches(fused: Partials, conv_w: torch.Tensor, conv_b: Optional[torch
     launches += 1 if taps > 1 else 0
 
 
+RGLRU_CHUNKED_FROM = 128     # a step whose longest portion has this many tokens runs the recurrence in chunks
+rglru_chunked = True         # tests switch the chunked form off to hold both against each other
+
+
 def rglru_scan(y: torch.Tensor, u: torch.Tensor, gr: torch.Tensor, gi: torch.Tensor, r_bias: Optional[torch.Tensor],
                i_bias: Optional[torch.Tensor], lam: torch.Tensor, rate: float, state: torch.Tensor, batch, out: torch.Tensor) -> None:
     """Per channel: r = sigmoid(gr + r_bias), i = sigmoid(gi + i_bias), a = exp(-rate r softplus(lam)),
-    S <- a S + sqrt(1 - a^2) i u, out = S y; S float32 at the start of each request's state slot."""
+    S <- a S + sqrt(1 - a^2) i u, out = S y; S float32 at the start of each request's state slot.  Steps that bring a
+    request `RGLRU_CHUNKED_FROM` tokens or more run the recurrence in chunks (two kernels; same result within rounding)."""
     T, C = y.shape
     for t, name in ((y, "y"), (u, "u"), (gr, "gr"), (gi, "gi")):
         _need(t, f"rglru_scan.{name}", torch.float32, 2)
@@ -1483,6 +1488,18 @@ def rglru_scan(y: torch.Tensor, u: torch.Tensor, gr: torch.Tensor, gi: torch.Ten
     _need(out, "rglru_scan.out", dims=2)
     if out.shape != (T, C) or lam.shape[0] != C:
         raise KernelError("rglru_scan: shapes differ")
+    if not batch.captured and batch.max_count >= RGLRU_CHUNKED_FROM and rglru_chunked:
+        # many tokens of a request: the recurrence in chunks, as many as keep the chip busy, of 32 tokens at least
+        chunk = max(32, (-(-int(batch.max_count) // 64) + 7) // 8 * 8)
+        chunks = -(-int(batch.max_count) // chunk)
+        scratch = torch.empty((batch.num_seqs * chunks * 2 * C,), dtype=torch.float32, device=y.device)
+        _check(library().kestrel_rglru_scan_chunked(y.data_ptr(), u.data_ptr(), gr.data_ptr(), gi.data_ptr(), _p(r_bias), _p(i_bias), lam.data_ptr(),
+                                                    float(rate), state.data_ptr(), state.stride(0), batch.cu_seqlens.data_ptr(),
+                                                    batch.slots.data_ptr(), out.data_ptr(), _code(out, "rglru_scan.out"), batch.num_seqs,
+                                                    int(batch.max_count), chunk, scratch.data_ptr(), C, _stream()))
+        global launches
+        launches += 1
+        return
     _check(library().kestrel_rglru_scan(y.data_ptr(), u.data_ptr(), gr.data_ptr(), gi.data_ptr(), _p(r_bias), _p(i_bias), lam.data_ptr(), float(rate),
                                         state.data_ptr(), state.stride(0), batch.cu_seqlens.data_ptr(), batch.slots.data_ptr(), out.data_ptr(),
                                         _code(out, "rglru_scan.out"), batch.num_seqs, C, _stream()))

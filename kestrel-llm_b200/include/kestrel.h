@@ -236,6 +236,8 @@ KESTREL_API int kestrel_delta_out(const float *o, const float *w, float eps, con
 /* ---- a diagonal recurrence with gates made from its own input (rglru.cu); state slot = [S: C | tail: (taps - 1) C] float32 ---- */
 KESTREL_API int kestrel_rglru_branches(const float *partial, int S, long long slice_stride, int ld, const float *bias, const float *conv_w, const float *conv_b, int taps, float *state, long long state_stride, long long tail_off, const int *seq_of_token, const int *cu_seqlens, const int *slots, float *y_out, float *u_out, void *u_st, int dtype, int T, int nseq, int C, kestrel_stream_t stream);
 KESTREL_API int kestrel_rglru_scan(const float *y, const float *u, const float *gr, const float *gi, const float *r_bias, const float *i_bias, const float *lam, float rate, float *state, long long state_stride, const int *cu_seqlens, const int *slots, void *out, int dtype, int nseq, int C, kestrel_stream_t stream);
+/* the same in chunks of `chunk` tokens (a multiple of 8) for steps that bring a request many tokens: two kernels, a thread a (request, chunk, channel); scratch float32 [nseq * ceil(max_count / chunk) * 2 * C] */
+KESTREL_API int kestrel_rglru_scan_chunked(const float *y, const float *u, const float *gr, const float *gi, const float *r_bias, const float *i_bias, const float *lam, float rate, float *state, long long state_stride, const int *cu_seqlens, const int *slots, void *out, int dtype, int nseq, int max_count, int chunk, float *scratch, int C, kestrel_stream_t stream);
 
 /* ---- linear recurrences S_t = diag(w) S + a (b^T S) + k v^T, o = S^T r per head (linear_recurrence.cu); S [H, d, dv] float32 at state_off of the request's state slot ---- */
 /* product columns q, f [n = H d] and v [nv = H dv]: r = silu(q), w = lower + (1 - lower) sigmoid(f + f_bias), k = 1 - w, v as it is; all float32 [T, .] */

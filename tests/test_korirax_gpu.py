@@ -235,6 +235,45 @@ def test_rotated_key_part_and_its_scale(dtype):
     assert f[0] == f0[0] and np.isclose(f[-1], f0[-1] / 16.0) and 0 < ((f < f0 * 0.99) & (f > f0 / 15.9)).sum() and mult > 1.2
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("layer", [K.rglru(64, 4, 4), K.rglru(42, 3, 2), K.rglru(264, 2, 3)], ids=["64", "42", "264"])
+def test_recurrence_in_chunks_and_token_by_token(dtype, layer):
+    """Portions of 128 tokens and more run the recurrence in chunks (a chunk's action on the state, then the chunks in
+    order); shorter ones and single tokens run it token by token.  Both against the plain statement over 700 tokens with
+    slow decays, the state handed from one form to the other and back; and the two forms against each other."""
+    from kestrel_llm_b200.csrc import ops
+
+    def prepare(W, h):
+        W["l0.mix.lam"][:] = np.linspace(-7.0, 1.0, W["l0.mix.lam"].shape[0])
+        return h.copy()
+    cuts = [3, 297, 1, 1, 130, 268]
+    got, want, _ = _mixer_case(layer, dtype, 16, 700, cuts, prepare=prepare)
+    _close(got, want, dtype, "chunks and single tokens")
+    ops.rglru_chunked = False
+    try:
+        seq, _, _ = _mixer_case(layer, dtype, 16, 700, cuts, prepare=prepare)
+    finally:
+        ops.rglru_chunked = True
+    _close(got, seq, dtype, "chunked against sequential", scale=float(np.abs(want).max()), tol={"float32": 1e-5, "bfloat16": 2e-2}[dtype])
+
+
+def test_recurrence_in_chunks_of_unequal_requests():
+    """Three requests in one step, 400, 129 and 2 tokens: the grid is sized by the longest, the others' chunks end early."""
+    layer = K.rglru(64, 4, 4)
+    rng = np.random.default_rng(3)
+    model, W, _ = _model_of([K.layer(layer, None)], 48, "float32", seed=3)
+    mixer = model.blocks[0].mixer
+    K.load_part(mixer, W)
+    Wr = K.bf16_round(W)
+    hs_ = [_exact(rng.standard_normal((n, 48))) for n in (430, 140, 5)]
+    want = [P.mix_rglru(h, Wr, "l0.mix.", layer["mixer"], 1e-6) for h in hs_]
+    hs = K.PartHarness(mixer, "float32", max_tokens=640, page_size=16, slots=3)
+    o1 = hs.step([(1, hs_[0][:400]), (2, hs_[1][:129]), (3, hs_[2][:2])])
+    o2 = hs.step([(3, hs_[2][2:5]), (1, hs_[0][400:430]), (2, hs_[1][129:140])])
+    for r, (a, b) in enumerate(((o1[0], o2[1]), (o1[1], o2[2]), (o1[2], o2[0]))):
+        _close(np.concatenate([a, b]), want[r], "float32", f"request {r}")
+
+
 def _ffn_case(mlp, dtype, n, seed=0, width=48, prepare=None):
     import torch
     model, W, _ = _model_of([K.layer(K.rglru(8, 1, 1), mlp)], width, dtype, seed=seed)
