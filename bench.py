@@ -339,7 +339,7 @@ KORIRAX_SIZES = {
 
 
 def korirax_raw(z):
-    att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5, "bias_max": 4096,
+    att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"], "scale": z["dim"] ** -0.5, "bias_max": 512,
            "bias_rows": z["rows"], "q_temp": {"coef": 0.1, "every": 1024}}
     lat = {"heads": z["l_heads"], "dim": z["l_dim"], "rot_dim": z["l_rot"], "vdim": z["l_vdim"], "q_rank": z["q_rank"], "kv_rank": z["kv_rank"],
            "scale": (z["l_dim"] + z["l_rot"]) ** -0.5,
@@ -500,7 +500,7 @@ def run_zidivik(args) -> int:
     L = len(raw["layers"])
     dense_raw = dict(QWEN3_8B, num_hidden_layers=L, hidden_size=z["width"], num_attention_heads=z["heads"],
                      num_key_value_heads=z["kv_heads"], head_dim=z["dim"],
-                     intermediate_size=(z["ff"] + (z["top"] * z["e_ff"] + z["shared"]) * 2 // 3) // 2 if korirax else
+                     intermediate_size=(z["ff"] + (z["top"] * z["e_ff"] + z["shared"]) * 2 // 3) // 2 // 256 * 256 if korirax else
                      z["ff"] * 2 // 3 if toredra else z["ff"] if tidavik else z["top"] * z["ff"],
                      vocab_size=z["vocab"], max_position_embeddings=8192)
     if tidavik:                              # the dense model's layers look through the same window

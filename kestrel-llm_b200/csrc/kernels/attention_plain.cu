@@ -9,7 +9,7 @@
 // The four warps of a block take keys lo+w, lo+w+4, ... in groups of four; their running
 // (max, sum, out) states are merged in warp order.  The order of every sum depends on
 // (lo, p) alone: a token's result is bit-identical however the step was cut or batched.
-// Works for any head size up to 256 and any numbers of heads.  It is the attention of the
+// Works for any head size up to 576 and any numbers of heads.  It is the attention of the
 // true 32-bit path and the twin that the fast kernels are tested against.
 //
 // Three options beyond the reference's attention, each off by default: `keep_first` tokens at
@@ -27,7 +27,7 @@
 #include <math.h>
 
 #define PA_WARPS 4
-#define PA_MAX_PER_LANE 8     // head size up to 256
+#define PA_MAX_PER_LANE 18    // head size up to 576 (a cached latent of 512 numbers beside a shared key part of 64)
 #define PA_KEYS 4
 
 template <typename T>

@@ -327,6 +327,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                     } else if (hs.cap > 0.f && hs.dist && sigmoid) {
 #pragma unroll
                         for (int j = 0; j < 128; ++j) sr[j] = __float_as_uint(hs.fast_as<true, true, true>(__uint_as_float(sr[j]) * p.scale, max(d0 - j, 0)));
+                    } else if (hs.rel && hs.cap == 0.f && !hs.dist && !sigmoid && !sink) {
+                        // a table of distance terms alone: one term for the whole tile where all of its keys lie beyond the table's
+                        // last distance, a look-up per score otherwise
+                        constexpr float LOG2E = 1.4426950408889634f;
+                        const float s2 = p.scale * LOG2E;
+                        if (d0 - 127 >= hs.rel_far) {
+                            const float add = hs.rel_of(hs.rel_far) * LOG2E;
+#pragma unroll
+                            for (int j = 0; j < 128; ++j) sr[j] = __float_as_uint(fmaf(__uint_as_float(sr[j]), s2, add));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 128; ++j) sr[j] = __float_as_uint(fmaf(__uint_as_float(sr[j]), s2, hs.rel_of(max(d0 - j, 0)) * LOG2E));
+                        }
                     } else {
 #pragma unroll
                         for (int j = 0; j < 128; ++j) {
@@ -529,8 +542,22 @@ KESTREL_API int kestrel_attention_tc_scored(const void *q, const void *k_cache, 
                                             int window, int slices, int slice_len, const int *max_kv_ptr, float scale, float softcap,
                                             const float *r1, const float *r2, const float *head_bias, int weighting, const float *sink,
                                             cudaStream_t stream) {
+    return kestrel_attention_tc_biased(q, k_cache, v_cache, out, part_o, part_ml, tile_seq, tile_row0, tiles, rows_per_tile, cu_seqlens, kv_lens,
+                                       block_table, table_width, table_stride, page_size, cache_pages, T, nq, nkv, hd, window, slices, slice_len,
+                                       max_kv_ptr, scale, softcap, r1, r2, head_bias, weighting, sink, nullptr, nullptr, 0, stream);
+}
+
+// The same with a learned number per head and bucket of distances added to the scores (ScoreOpts.rel)
+KESTREL_API int kestrel_attention_tc_biased(const void *q, const void *k_cache, const void *v_cache, void *out,
+                                            float *part_o, float *part_ml, const int *tile_seq, const int *tile_row0,
+                                            int tiles, int rows_per_tile, const int *cu_seqlens, const int *kv_lens, const int *block_table,
+                                            int table_width, int table_stride, int page_size, int cache_pages, int T, int nq, int nkv, int hd,
+                                            int window, int slices, int slice_len, const int *max_kv_ptr, float scale, float softcap,
+                                            const float *r1, const float *r2, const float *head_bias, int weighting, const float *sink,
+                                            const float *rel, const int *rel_bucket, int rel_far, cudaStream_t stream) {
     if (T == 0 || tiles == 0) return 0;
-    const bool scored = softcap > 0.f || r1 != nullptr || weighting != KESTREL_WEIGH_SOFTMAX;
+    KESTREL_REQUIRE(!rel || (rel_bucket && rel_far >= 0), "attention_tc: a distance table without its buckets");
+    const bool scored = softcap > 0.f || r1 != nullptr || rel != nullptr || weighting != KESTREL_WEIGH_SOFTMAX;
     KESTREL_REQUIRE(weighting >= 0 && weighting <= 2 && softcap >= 0.f && (r1 == nullptr) == (r2 == nullptr), "attention_tc: bad score options");
     KESTREL_REQUIRE(!scored || slices == 1 || (weighting != KESTREL_WEIGH_SIGMOID && (weighting != KESTREL_WEIGH_SOFTMAX_SINK || sink)),
                     "attention_tc: sigmoid weights, and an extra term without its numbers, go with one slice of keys, not %d", slices);
@@ -556,7 +583,7 @@ KESTREL_API int kestrel_attention_tc_scored(const void *q, const void *k_cache, 
     p.max_kv_ptr = max_kv_ptr;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.scale = scale;
-    p.opts = {softcap, r1, r2, head_bias, weighting, sink};
+    p.opts = {softcap, r1, r2, head_bias, weighting, sink, rel, rel_bucket, rel_far, nq};
     p.scored = scored ? 1 : 0;
     size_t smem = 12 * AT_PANEL + 8 * B_COUNT + 16 + 1024;
     static bool attr_set = false;

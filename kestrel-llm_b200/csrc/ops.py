@@ -590,11 +590,12 @@ def attention_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
         part_o = torch.empty((T * nq, slices, hd), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((T * nq, slices, 2), dtype=torch.float32, device=q.device)
     slice_len = min(int(slice_len), (1 << 30) // 128 * 128)
-    _check(library().kestrel_attention_tc_scored(
+    _check(library().kestrel_attention_tc_biased(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _p(part_o), _p(part_ml),
         tile_seq.data_ptr(), tile_row0.data_ptr(), tiles, int(rows_per_tile), cu_seqlens.data_ptr(), kv_lens.data_ptr(),
         block_table.data_ptr(), block_table.shape[1], block_table.stride(0), int(page_size), int(k_cache.shape[0]), T, nq, nkv, hd,
-        int(window), int(slices), slice_len, _p(max_kv_dev), float(scale), *(score or ScoreOptions()).args(nq), _stream()))
+        int(window), int(slices), slice_len, _p(max_kv_dev), float(scale), *(score or ScoreOptions()).args(nq), *(score or ScoreOptions()).rel_args(nq),
+        _stream()))
     if slices > 1:
         global launches
         launches += 1          # the merge kernel

@@ -205,6 +205,7 @@ KESTREL_API int kestrel_attention_window_biased(const void *q, const void *k_cac
 KESTREL_API int kestrel_attention_window_splits(int nseq, int max_count, int nq, int nkv, int hd, int vd, int window, int max_kv_len);
 KESTREL_API long long kestrel_attention_window_scratch_floats(int nseq, int max_count, int nq, int nkv, int hd, int vd, int ksplit);
 KESTREL_API int kestrel_attention_tc_scored(const void *q, const void *k_cache, const void *v_cache, void *out, float *part_o, float *part_ml, const int *tile_seq, const int *tile_row0, int tiles, int rows_per_tile, const int *cu_seqlens, const int *kv_lens, const int *block_table, int table_width, int table_stride, int page_size, int cache_pages, int T, int nq, int nkv, int hd, int window, int slices, int slice_len, const int *max_kv_ptr, float scale, float softcap, const float *r1, const float *r2, const float *head_bias, int weighting, const float *sink, kestrel_stream_t stream);
+KESTREL_API int kestrel_attention_tc_biased(const void *q, const void *k_cache, const void *v_cache, void *out, float *part_o, float *part_ml, const int *tile_seq, const int *tile_row0, int tiles, int rows_per_tile, const int *cu_seqlens, const int *kv_lens, const int *block_table, int table_width, int table_stride, int page_size, int cache_pages, int T, int nq, int nkv, int hd, int window, int slices, int slice_len, const int *max_kv_ptr, float scale, float softcap, const float *r1, const float *r2, const float *head_bias, int weighting, const float *sink, const float *rel, const int *rel_bucket, int rel_far, kestrel_stream_t stream);
 /* attn_prepare_ex with a bias per product column (NULL: none); qk_norm 0: none, 1: per head (weights [hd] or NULL), 2: over the whole q and the whole k projection (weights [nq hd], [nkv hd]); v_norm: v / sqrt(mean(v^2) + eps) per head */
 KESTREL_API int kestrel_attn_prepare_normed(const float *partial, int S, long long slice_stride, int ld, const float *bias, const float *q_norm_w, const float *k_norm_w, int qk_norm, int v_norm, float norm_eps, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *k_cache, void *v_cache, void *q_out, float *gate_out, int dtype, int T, int nq, int nkv, int hd, int vd, int has_kv, kestrel_stream_t stream);
 /* attn_prepare_normed, then q and k turned by position where inv_freq is given: pair j of a head's first `rot` dimensions by position * inv_freq[j]; rot_mode 0 pairs j with j + rot / 2, 1 pairs 2j with 2j + 1; rot_scale multiplies cos and sin */

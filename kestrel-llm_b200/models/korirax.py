@@ -74,7 +74,7 @@ def build_korirax(config: KoriraxConfig, dtype: torch.dtype, device) -> DecoderM
     rows = StreamRows(c.loop_passes, W, device, "loop.step") if c.loop_passes else None
     return DecoderModel(c, dtype, device, emb, None, blocks, order, RMSNorm(W, eps, device, "final.norm"),
                         LMHead(c.vocab_size, W, dtype, device, "head"), shared_parts=[table] if table is not None else [],
-                        stream_rows=rows)
+                        stream_rows=rows, optional_tensors=[] if rows is not None else ["loop.step"])
 
 
 register_architecture(NAME, KoriraxConfig, build_korirax)

@@ -179,7 +179,7 @@ class GatedWindowAttention(Mixer):
         a = torch.empty((T, self.heads * self.v_head_dim), dtype=self.dtype, device=x.device)
         G = self.heads // self.kv_heads
         if self.dtype == torch.bfloat16 and not self.force_plain and self.tcgen05 and self.head_dim == self.v_head_dim == 128 and \
-                gate is None and self.rel is None and self.keep_first == 0 and not batch.captured and batch.max_count * G > self.TC_MIN_ROWS and \
+                gate is None and self.keep_first == 0 and not batch.captured and batch.max_count * G > self.TC_MIN_ROWS and \
                 ops.attention_tc_supported(128, cache.page_size):
             # prompt portions of head size 128: the tcgen05 kernel, rows in tiles of 256 per request
             tile_seq, tile_row0 = ops.row_tiles(batch, G, 256)

@@ -53,8 +53,9 @@ class LatentAttention(Mixer):
     def __init__(self, width: int, heads: int, head_dim: int, v_head_dim: int, q_rank: int, kv_rank: int, dtype: torch.dtype, device,
                  prefix: str, scale: float, norm_eps: float, window: int = 0, head_gate: bool = True,
                  names=("dq", "uq", "dkv", "uk", "uv", "g", "o"), rot_dim: int = 0, position=None, element_gate: bool = False):
-        if kv_rank + rot_dim > 256:
-            raise ValueError(f"a cached row of {kv_rank} + {rot_dim} numbers: the attention kernels take head sizes up to 256")
+        if kv_rank + rot_dim > 576:
+            raise ValueError(f"a cached row of {kv_rank} + {rot_dim} numbers: the plain attention kernel takes head sizes up to 576 "
+                             f"(the tensor-core kernels up to 256)")
         if element_gate and head_gate:
             raise ValueError("a gate per head or a gate per element, not both")
         self.rot_dim, self.element_gate = int(rot_dim), bool(element_gate)

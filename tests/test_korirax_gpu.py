@@ -96,6 +96,7 @@ MIXERS = [
     ("latent 2 x 64+64/128, ranks 48/192", K.latent(2, 64, 64, 128, 48, 192, 0.1, 64, 100000.0, (16.0, 128, 16.0, 2.0))),
     ("latent 4 x 32+16/32, ranks 64/80", K.latent(4, 32, 16, 32, 64, 80, 0.15, 16, 1000.0, (4.0, 96, 8.0, 1.0))),
     ("latent 1 x 8+2/8, ranks 8/8", K.latent(1, 8, 2, 8, 8, 8, 0.4, 2, 10.0)),
+    ("latent 2 x 16+16/16, ranks 24/272 (a cache row beyond the tensor-core kernels' sizes)", K.latent(2, 16, 16, 16, 24, 272, 0.2, 16, 100.0, RAMP)),
     ("recurrence 64 in 4 blocks, 4 taps", K.rglru(64, 4, 4)),
     ("recurrence 42 in 3 blocks, 2 taps", K.rglru(42, 3, 2)),
     ("recurrence 256 in 1 block, 1 tap", K.rglru(256, 1, 1)),
@@ -203,6 +204,20 @@ def test_distance_terms_by_bucket_and_beyond_the_last(dtype, decode):
     half = rows // 2
     edges = [n_ for n_ in range(1, 200) if P.distance_bucket(n_, rows, far) != P.distance_bucket(n_ - 1, rows, far)]
     assert edges[:half] == list(range(1, half + 1)) and P.distance_bucket(far, rows, far) == rows - 1 == P.distance_bucket(10 * far, rows, far)
+
+
+@pytest.mark.parametrize("cuts", [[700], [300, 400], [520, 2, 178]])
+def test_distance_terms_in_portions_of_head_size_128(cuts):
+    """bfloat16 portions of head size 128 take the tcgen05 kernel: key tiles near the diagonal look every score's term up,
+    tiles that lie wholly beyond the table's last distance take one term; later portions cut their keys into slices."""
+    layer = K.attn(4, 2, 128, 128, 0.09, 60, 12, (0.5, 64))
+
+    def prepare(W, h):
+        W["l0.mix.rel"][:] *= 3.0
+        W["l0.mix.rel"][-1, :] = np.array([4.0, -4.0, 2.0, 0.0])
+        return h.copy()
+    got, want, _ = _mixer_case(layer, "bfloat16", 16, 700, cuts, prepare=prepare)
+    _close(got, want, "bfloat16", f"portions {cuts}")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
