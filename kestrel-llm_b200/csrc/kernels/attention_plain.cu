@@ -35,7 +35,7 @@ __global__ void __launch_bounds__(PA_WARPS * 32)
 attention_plain_kernel(const T *__restrict__ q, const T *__restrict__ k_cache, const T *__restrict__ v_cache,
                        const int *__restrict__ positions, const int *__restrict__ seq_of_token,
                        const int *__restrict__ block_table, int table_stride, int page_size,
-                       T *__restrict__ out, int nq, int nkv, int hd, int vd, int window, int keep_first,
+                       T *__restrict__ out, int nq, int nkv, int hd, int vd, int v_ld, int window, int keep_first,
                        const float *__restrict__ gate, float scale, const ScoreOpts opts) {
     pdl_launch_dependents();
     pdl_wait();
@@ -74,7 +74,7 @@ attention_plain_kernel(const T *__restrict__ q, const T *__restrict__ k_cache, c
                 int page = table[s / page_size];
                 size_t row = ((size_t)page * nkv + kvh) * page_size + (s % page_size);
                 const T *krow = k_cache + row * hd;
-                vrow[u] = v_cache + row * vd;
+                vrow[u] = v_cache + row * v_ld;
 #pragma unroll
                 for (int c = 0; c < PA_MAX_PER_LANE; ++c) {
                     int i = lane + 32 * c;
@@ -168,20 +168,22 @@ KESTREL_API int kestrel_attention_plain_scored(const void *q, const void *k_cach
                                                const float *r2, const float *head_bias, int weighting, const float *sink,
                                                cudaStream_t stream) {
     return kestrel_attention_plain_biased(q, k_cache, v_cache, positions, seq_of_token, block_table, table_stride, page_size, out, dtype, T, nq, nkv,
-                                          hd, vd, window, keep_first, gate, scale, softcap, r1, r2, head_bias, weighting, sink, nullptr, nullptr, 0,
+                                          hd, vd, window, keep_first, gate, scale, softcap, r1, r2, head_bias, weighting, sink, nullptr, nullptr, 0, 0,
                                           stream);
 }
 
 // the same with a learned number per head and bucket of distances added to the scores: rel [buckets, nq], the bucket of
-// a distance from rel_bucket [rel_far + 1] (distances beyond rel_far share its bucket)
+// a distance from rel_bucket [rel_far + 1] (distances beyond rel_far share its bucket); `v_ld` > 0: the V plane's rows hold v_ld
+// numbers of which the first vd are the value (a V plane that is the K plane of longer rows)
 KESTREL_API int kestrel_attention_plain_biased(const void *q, const void *k_cache, const void *v_cache,
                                                const int *positions, const int *seq_of_token,
                                                const int *block_table, int table_stride, int page_size,
                                                void *out, int dtype, int T, int nq, int nkv, int hd, int vd, int window,
                                                int keep_first, const float *gate, float scale, float softcap, const float *r1,
                                                const float *r2, const float *head_bias, int weighting, const float *sink,
-                                               const float *rel, const int *rel_bucket, int rel_far, cudaStream_t stream) {
+                                               const float *rel, const int *rel_bucket, int rel_far, int v_ld, cudaStream_t stream) {
     if (T == 0) return 0;
+    KESTREL_REQUIRE(v_ld == 0 || v_ld >= vd, "attention_plain: value rows of %d numbers for values of %d", v_ld, vd);
     KESTREL_REQUIRE(weighting >= 0 && weighting <= 2 && softcap >= 0.f && (r1 == nullptr) == (r2 == nullptr), "attention_plain: bad score options");
     KESTREL_REQUIRE(!rel || (rel_bucket && rel_far >= 0), "attention_plain: a distance table without its buckets");
     const ScoreOpts opts = {softcap, r1, r2, head_bias, weighting, sink, rel, rel_bucket, rel_far, nq};
@@ -191,10 +193,10 @@ KESTREL_API int kestrel_attention_plain_biased(const void *q, const void *k_cach
     dim3 grid(T, nq);
     if (dtype == KESTREL_F32)
         kestrel_launch(attention_plain_kernel<float>, dim3(grid), dim3(PA_WARPS * 32), 0, stream, (const float *)q, (const float *)k_cache, (const float *)v_cache, positions, seq_of_token,
-            block_table, table_stride, page_size, (float *)out, nq, nkv, hd, vd, window, keep_first, gate, scale, opts);
+            block_table, table_stride, page_size, (float *)out, nq, nkv, hd, vd, v_ld > 0 ? v_ld : vd, window, keep_first, gate, scale, opts);
     else if (dtype == KESTREL_BF16)
         kestrel_launch(attention_plain_kernel<__nv_bfloat16>, dim3(grid), dim3(PA_WARPS * 32), 0, stream, (const __nv_bfloat16 *)q, (const __nv_bfloat16 *)k_cache, (const __nv_bfloat16 *)v_cache, positions,
-            seq_of_token, block_table, table_stride, page_size, (__nv_bfloat16 *)out, nq, nkv, hd, vd, window, keep_first, gate, scale, opts);
+            seq_of_token, block_table, table_stride, page_size, (__nv_bfloat16 *)out, nq, nkv, hd, vd, v_ld > 0 ? v_ld : vd, window, keep_first, gate, scale, opts);
     else
         return kestrel_fail(-2, "attention_plain: unknown dtype %d", dtype);
     return kestrel_check_launch("attention_plain");

@@ -45,7 +45,8 @@
 struct AwParams {
     const __nv_bfloat16 *q;         // [T, nq * hd]
     const __nv_bfloat16 *k_cache;   // [pages, nkv, page_size, hd]
-    const __nv_bfloat16 *v_cache;   // [pages, nkv, page_size, vd]
+    const __nv_bfloat16 *v_cache;   // [pages, nkv, page_size, v_ld]: a value is the first vd numbers of its row (v_ld = vd unless the rows hold more)
+    int v_ld;
     __nv_bfloat16 *out;             // [T, nq * vd]
     const float *gate;              // [T, nq] or null
     const int *cu_seqlens, *kv_lens, *block_table;
@@ -108,7 +109,7 @@ attention_window_kernel(const AwParams p) {
             if (in) row = ((size_t)table[s / p.page_size] * p.nkv + kvh) * p.page_size + (s % p.page_size);
             const bool k_ok = in && c * 8 < hd, v_ok = in && c * 8 < vd;
             aw_cp_async16((uint32_t)__cvta_generic_to_shared(Ks + ((size_t)slot * AW_BN + r) * LDS + c * 8), p.k_cache + (k_ok ? row * hd + c * 8 : 0), k_ok);
-            aw_cp_async16((uint32_t)__cvta_generic_to_shared(Vs + ((size_t)slot * AW_BN + r) * LDS + c * 8), p.v_cache + (v_ok ? row * vd + c * 8 : 0), v_ok);
+            aw_cp_async16((uint32_t)__cvta_generic_to_shared(Vs + ((size_t)slot * AW_BN + r) * LDS + c * 8), p.v_cache + (v_ok ? row * p.v_ld + c * 8 : 0), v_ok);
         }
     };
     auto load_round = [&](int rd) {                   // the KW tiles of round rd, into the slots of its parity
@@ -458,17 +459,18 @@ KESTREL_API int kestrel_attention_window_scored(const void *q, const void *k_cac
                                                 float softcap, const float *r1, const float *r2, const float *head_bias, int weighting,
                                                 const float *sink, int ksplit, float *scratch, cudaStream_t stream) {
     return kestrel_attention_window_biased(q, k_cache, v_cache, out, gate, cu_seqlens, kv_lens, block_table, table_stride, page_size, nseq, max_count,
-                                           nq, nkv, hd, vd, window, keep_first, scale, softcap, r1, r2, head_bias, weighting, sink, nullptr, nullptr, 0,
+                                           nq, nkv, hd, vd, window, keep_first, scale, softcap, r1, r2, head_bias, weighting, sink, nullptr, nullptr, 0, 0,
                                            ksplit, scratch, stream);
 }
 
-// the same with a learned number per head and bucket of distances added to the scores (ScoreOpts.rel)
+// the same with a learned number per head and bucket of distances added to the scores (ScoreOpts.rel), and with value rows of
+// `v_ld` numbers of which the first vd are the value (0: vd) - a V plane that is the K plane of longer rows
 KESTREL_API int kestrel_attention_window_biased(const void *q, const void *k_cache, const void *v_cache, void *out, const float *gate,
                                                 const int *cu_seqlens, const int *kv_lens, const int *block_table, int table_stride, int page_size,
                                                 int nseq, int max_count, int nq, int nkv, int hd, int vd, int window, int keep_first, float scale,
                                                 float softcap, const float *r1, const float *r2, const float *head_bias, int weighting,
-                                                const float *sink, const float *rel, const int *rel_bucket, int rel_far, int ksplit,
-                                                float *scratch, cudaStream_t stream) {
+                                                const float *sink, const float *rel, const int *rel_bucket, int rel_far, int v_ld,
+                                                int ksplit, float *scratch, cudaStream_t stream) {
     if (nseq == 0 || max_count == 0) return 0;
     KESTREL_REQUIRE(ksplit >= 1 && ksplit <= 65535 && (ksplit == 1 || scratch), "attention_window: %d shares of the keys without scratch", ksplit);
     KESTREL_REQUIRE(weighting >= 0 && weighting <= 2 && softcap >= 0.f && (r1 == nullptr) == (r2 == nullptr), "attention_window: bad score options");
@@ -489,11 +491,13 @@ KESTREL_API int kestrel_attention_window_biased(const void *q, const void *k_cac
     p.nkv = nkv;
     p.hd = hd;
     p.vd = vd;
+    p.v_ld = v_ld > 0 ? v_ld : vd;
     p.window = window;
     p.keep_first = window > 0 ? keep_first : 0;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.scale = scale;
     KESTREL_REQUIRE(!rel || (rel_bucket && rel_far >= 0), "attention_window: a distance table without its buckets");
+    KESTREL_REQUIRE(v_ld == 0 || (v_ld >= vd && v_ld % 8 == 0), "attention_window: value rows of %d numbers for values of %d", v_ld, vd);
     p.opts = {softcap, r1, r2, head_bias, weighting, sink, rel, rel_bucket, rel_far, nq};
     p.scored = softcap > 0.f || r1 != nullptr || rel != nullptr || weighting != KESTREL_WEIGH_SOFTMAX;
     const int D = max(hd, vd), G = nq / nkv;

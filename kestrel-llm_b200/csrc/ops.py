@@ -1029,8 +1029,8 @@ _NO_SCORE = ScoreOptions()
 def attention_plain_ex(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, positions: torch.Tensor,
                        seq_of_token: torch.Tensor, block_table: torch.Tensor, page_size: int, out: torch.Tensor, nq: int, nkv: int,
                        hd: int, vd: int, window: int, keep_first: int, gate: Optional[torch.Tensor], scale: float,
-                       score: Optional[ScoreOptions] = None) -> None:
-    """`attention_plain` with values of size ``vd``, the first ``keep_first`` keys of a request
+                       score: Optional[ScoreOptions] = None, v_ld: int = 0) -> None:
+    """`attention_plain` with values of size ``vd`` (the first ``vd`` numbers of V rows of ``v_ld``, where that is given), the first ``keep_first`` keys of a request
     visible beyond the window, each head's output multiplied by ``gate`` [T, nq], and the layer's
     `ScoreOptions`."""
     _need(q, "attention.q", dims=2)
@@ -1046,7 +1046,7 @@ def attention_plain_ex(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
     _check(library().kestrel_attention_plain_biased(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
         block_table.stride(0), int(page_size), out.data_ptr(), _code(q, "attention.q"), T, nq, nkv, hd, vd, int(window), int(keep_first),
-        _p(gate), float(scale), *(score or _NO_SCORE).args(nq), *(score or _NO_SCORE).rel_args(nq), _stream()))
+        _p(gate), float(scale), *(score or _NO_SCORE).args(nq), *(score or _NO_SCORE).rel_args(nq), int(v_ld), _stream()))
 
 
 def attention_window_supported(hd: int, vd: int, nq: int, nkv: int) -> bool:
@@ -1056,7 +1056,7 @@ def attention_window_supported(hd: int, vd: int, nq: int, nkv: int) -> bool:
 
 def attention_window(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, batch, block_table: torch.Tensor, page_size: int,
                      out: torch.Tensor, nq: int, nkv: int, hd: int, vd: int, window: int, keep_first: int, gate: Optional[torch.Tensor],
-                     scale: float, score: Optional[ScoreOptions] = None) -> None:
+                     scale: float, score: Optional[ScoreOptions] = None, v_ld: int = 0) -> None:
     """`attention_plain_ex` for bfloat16 on the tensor cores, over this step's requests as ``batch``
     describes them (cumulative lengths, lengths after the step, the most tokens of one request and the
     longest context).  A step of single tokens cuts its key rounds into shares, a CTA each, and a
@@ -1069,7 +1069,7 @@ def attention_window(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     T = q.shape[0]
     if q.shape[1] != nq * hd or out.shape != (T, nq * vd) or T != batch.num_tokens:
         raise KernelError("attention_window: shapes differ")
-    if tuple(k_cache.shape[1:]) != (nkv, page_size, hd) or tuple(v_cache.shape[1:]) != (nkv, page_size, vd):
+    if tuple(k_cache.shape[1:]) != (nkv, page_size, hd) or tuple(v_cache.shape[1:]) != (nkv, page_size, v_ld or vd):
         raise KernelError("attention_window: the cache planes do not fit the heads")
     if gate is not None:
         _need(gate, "attention_window.gate", torch.float32, 2)
@@ -1083,7 +1083,7 @@ def attention_window(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     _check(lib.kestrel_attention_window_biased(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _p(gate), batch.cu_seqlens.data_ptr(), batch.kv_lens.data_ptr(),
         block_table.data_ptr(), block_table.stride(0), int(page_size), int(batch.num_seqs), int(batch.max_count), nq, nkv, hd, vd, int(window),
-        int(keep_first), float(scale), *(score or _NO_SCORE).args(nq), *(score or _NO_SCORE).rel_args(nq), ksplit, _p(scratch), _stream()))
+        int(keep_first), float(scale), *(score or _NO_SCORE).args(nq), *(score or _NO_SCORE).rel_args(nq), int(v_ld), ksplit, _p(scratch), _stream()))
     if ksplit > 1:
         global launches
         launches += 1          # the merge kernel

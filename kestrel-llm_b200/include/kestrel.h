@@ -197,10 +197,10 @@ KESTREL_API int kestrel_attention_window(const void *q, const void *k_cache, con
    weighting 0: softmax; 1: softmax with a valueless extra term exp(sink[h]) in the denominator (sink [nq], or NULL for
    exp(0)); 2: every visible key weighs sigmoid(s + head_bias[h]) (head_bias [nq] or NULL), not normalised over keys */
 KESTREL_API int kestrel_attention_plain_scored(const void *q, const void *k_cache, const void *v_cache, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *out, int dtype, int T, int nq, int nkv, int hd, int vd, int window, int keep_first, const float *gate, float scale, float softcap, const float *r1, const float *r2, const float *head_bias, int weighting, const float *sink, kestrel_stream_t stream);
-/* the same with rel[bucket[min(i - j, rel_far)], head] added to the scores: rel float32 [buckets, nq], rel_bucket int32 [rel_far + 1] (rel may be NULL) */
-KESTREL_API int kestrel_attention_plain_biased(const void *q, const void *k_cache, const void *v_cache, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *out, int dtype, int T, int nq, int nkv, int hd, int vd, int window, int keep_first, const float *gate, float scale, float softcap, const float *r1, const float *r2, const float *head_bias, int weighting, const float *sink, const float *rel, const int *rel_bucket, int rel_far, kestrel_stream_t stream);
+/* the same with rel[bucket[min(i - j, rel_far)], head] added to the scores: rel float32 [buckets, nq], rel_bucket int32 [rel_far + 1] (rel may be NULL); v_ld > 0: the V plane's rows hold v_ld numbers, the first vd of them the value */
+KESTREL_API int kestrel_attention_plain_biased(const void *q, const void *k_cache, const void *v_cache, const int *positions, const int *seq_of_token, const int *block_table, int table_stride, int page_size, void *out, int dtype, int T, int nq, int nkv, int hd, int vd, int window, int keep_first, const float *gate, float scale, float softcap, const float *r1, const float *r2, const float *head_bias, int weighting, const float *sink, const float *rel, const int *rel_bucket, int rel_far, int v_ld, kestrel_stream_t stream);
 KESTREL_API int kestrel_attention_window_scored(const void *q, const void *k_cache, const void *v_cache, void *out, const float *gate, const int *cu_seqlens, const int *kv_lens, const int *block_table, int table_stride, int page_size, int nseq, int max_count, int nq, int nkv, int hd, int vd, int window, int keep_first, float scale, float softcap, const float *r1, const float *r2, const float *head_bias, int weighting, const float *sink, int ksplit, float *scratch, kestrel_stream_t stream);
-KESTREL_API int kestrel_attention_window_biased(const void *q, const void *k_cache, const void *v_cache, void *out, const float *gate, const int *cu_seqlens, const int *kv_lens, const int *block_table, int table_stride, int page_size, int nseq, int max_count, int nq, int nkv, int hd, int vd, int window, int keep_first, float scale, float softcap, const float *r1, const float *r2, const float *head_bias, int weighting, const float *sink, const float *rel, const int *rel_bucket, int rel_far, int ksplit, float *scratch, kestrel_stream_t stream);
+KESTREL_API int kestrel_attention_window_biased(const void *q, const void *k_cache, const void *v_cache, void *out, const float *gate, const int *cu_seqlens, const int *kv_lens, const int *block_table, int table_stride, int page_size, int nseq, int max_count, int nq, int nkv, int hd, int vd, int window, int keep_first, float scale, float softcap, const float *r1, const float *r2, const float *head_bias, int weighting, const float *sink, const float *rel, const int *rel_bucket, int rel_far, int v_ld, int ksplit, float *scratch, kestrel_stream_t stream);
 /* a step of single tokens may cut its key rounds into `ksplit` shares, a CTA each, merged by a second kernel; scratch of kestrel_attention_window_scratch_floats floats */
 KESTREL_API int kestrel_attention_window_splits(int nseq, int max_count, int nq, int nkv, int hd, int vd, int window, int max_kv_len);
 KESTREL_API long long kestrel_attention_window_scratch_floats(int nseq, int max_count, int nq, int nkv, int hd, int vd, int ksplit);

@@ -14,8 +14,9 @@ Heads are not rotated unless the mixer is built with ``rot_dim`` > 0: a head's q
 its ``d`` unrotated ones, W_dkv has ``rot_dim`` more rows behind the latent's - one key part that ALL heads share, not normed -,
 both are turned by position as ``position`` (a `PositionEncoding` with a `rotary()`) says, and the score is
 (q_n[:d] . k_nj + q_n[d:] . kr_j) * scale.  The cache row of a token is then [c | kr], and the query that meets it
-[Uk_n^T q_n[:d] | q_n[d:]]: attention still runs over the cache rows themselves, as one key/value head of kv_rank + rot_dim
-numbers whose first kv_rank are the value (the mixed rows' last rot_dim columns are not used).  ``element_gate``: the gate is a
+[Uk_n^T q_n[:d] | q_n[d:]]: attention still runs over the cache rows themselves, as one key/value head whose keys are the rows
+of kv_rank + rot_dim numbers and whose values are the rows' first kv_rank (the kernels take the V plane's row length apart from
+the value size).  ``element_gate``: the gate is a
 number per element of the concatenated heads instead of one per head.
 
 Since q_n . k_nj = (Uk_n^T q_n) . c_j and sum_j p_j v_nj = Uv_n sum_j p_j c_j,
@@ -114,13 +115,15 @@ class LatentAttention(Mixer):
             ops.latent_rotate_queries(q, H, d, self.rot_dim, q_lat, R, batch.positions, self.rotation)
         else:
             q_lat = ops.head_gemm(q, self.up_k_w, H, w_kn=True)                # [T, H kv_rank]: Uk_n^T q_n
-        a = torch.empty((T, H * D), dtype=self.dtype, device=x.device)
-        if self.dtype == torch.bfloat16 and not self.force_plain and ops.attention_window_supported(D, D, H, 1):
-            ops.attention_window(q_lat, cache.k, cache.k, batch, table, cache.page_size, a, H, 1, D, D, self.window, 0, gate, self.scale)
+        # keys are whole cache rows, values their first kv_rank numbers: the V plane is the K plane with rows of D numbers
+        a = torch.empty((T, H * R), dtype=self.dtype, device=x.device)
+        if self.dtype == torch.bfloat16 and not self.force_plain and ops.attention_window_supported(D, R, H, 1):
+            ops.attention_window(q_lat, cache.k, cache.k, batch, table, cache.page_size, a, H, 1, D, R, self.window, 0, gate, self.scale,
+                                 v_ld=D)
         else:
-            ops.attention_plain_ex(q_lat, cache.k, cache.k, batch.positions, batch.seq_of_token, table, cache.page_size, a, H, 1, D, D,
-                                   self.window, 0, gate, self.scale)
-        o = ops.head_gemm(a, self.up_v_w, H, w_kn=False, x_head_stride=D)      # [T, H dv]: Uv_n (mixed latent)
+            ops.attention_plain_ex(q_lat, cache.k, cache.k, batch.positions, batch.seq_of_token, table, cache.page_size, a, H, 1, D, R,
+                                   self.window, 0, gate, self.scale, v_ld=D)
+        o = ops.head_gemm(a, self.up_v_w, H, w_kn=False)                       # [T, H dv]: Uv_n (mixed latent)
         if self.element_gate:
             ops.gate_columns_mul(o, fused, self.q_rank + self.row)
         return self.out.forward(o, residual=residual)      # many tokens: the product adds itself to the stream
