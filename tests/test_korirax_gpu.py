@@ -206,7 +206,7 @@ def test_distance_terms_by_bucket_and_beyond_the_last(dtype, decode):
     assert edges[:half] == list(range(1, half + 1)) and P.distance_bucket(far, rows, far) == rows - 1 == P.distance_bucket(10 * far, rows, far)
 
 
-@pytest.mark.parametrize("cuts", [[700], [300, 400], [520, 2, 178]])
+@pytest.mark.parametrize("cuts", [[700], [300, 400], [520, 2, 178], [900, 400]])
 def test_distance_terms_in_portions_of_head_size_128(cuts):
     """bfloat16 portions of head size 128 take the tcgen05 kernel: key tiles near the diagonal look every score's term up,
     tiles that lie wholly beyond the table's last distance take one term; later portions cut their keys into slices."""
@@ -216,7 +216,7 @@ def test_distance_terms_in_portions_of_head_size_128(cuts):
         W["l0.mix.rel"][:] *= 3.0
         W["l0.mix.rel"][-1, :] = np.array([4.0, -4.0, 2.0, 0.0])
         return h.copy()
-    got, want, _ = _mixer_case(layer, "bfloat16", 16, 700, cuts, prepare=prepare)
+    got, want, _ = _mixer_case(layer, "bfloat16", 16, sum(cuts), cuts, prepare=prepare)
     _close(got, want, "bfloat16", f"portions {cuts}")
 
 
